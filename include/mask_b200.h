@@ -1,0 +1,197 @@
+/*
+ * mask_b200 -- C ABI of the B200 (sm_100a) SpMM engine for the SR-BCRS 16x8 and ME-TCF formats.
+ *
+ * C = A * B with A sparse FP32 packed into dense 16x8 tiles of window-condensed columns,
+ * B dense FP32 row-major with N columns, TF32 tensor-core products (both operands rounded to
+ * nearest, ties away, like cvt.rna.tf32.f32) and FP32 accumulation.
+ *
+ * Conventions
+ *   - every function returns a mask_status (0 = success); nothing throws or aborts;
+ *     mask_last_error() gives a per-thread message for the last failure.
+ *   - pointers named d_* are device pointers on the current CUDA device, h_* are host pointers.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
+ *   - sizes that can pass 2^31 (tile counts times 128, M*N) are 64-bit.
+ *   - W = ceil(M/16) row windows, T = number of 16x8 tiles.
+ *
+ * Each entry point cites the interface of the reference project (hd9568/MASK) that it replaces,
+ * as a path inside that project.
+ */
+#ifndef MASK_B200_H_
+#define MASK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum mask_status {
+    MASK_OK = 0,
+    MASK_ERR_INVALID_ARGUMENT = 1, /* null pointer, negative size, N not a multiple of 4, ... */
+    MASK_ERR_CUDA = 2,             /* a CUDA runtime call failed; see mask_last_error() */
+    MASK_ERR_UNSORTED_ROWS = 3,    /* CSR rows must hold strictly ascending column ids */
+    MASK_ERR_SCRATCH_TOO_SMALL = 4,
+    MASK_ERR_INDEX_OVERFLOW = 5,   /* a count does not fit the int32 index arrays of the format */
+    MASK_ERR_COLUMN_RANGE = 6,     /* a column id is outside [0, K) */
+    MASK_ERR_NO_DEVICE = 7
+} mask_status;
+
+int mask_version(void);
+const char* mask_status_string(int status);
+const char* mask_last_error(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Format builder (device).  Replaces the host packers convertToSRBCRS
+ * (examples/src_fp32/sr_bcrs/testbed/main_16x8.cu:196-328), its extension twin
+ * preprocess_gpu_srcfp32_srbcrs (examples/src_fp32/sr_bcrs/testbed/SRBCRSSpMM_kernel.cu:172-393)
+ * and buildMETCFMetadata (examples/src_fp32/dtc/testbed/main.cu:352-520).  Output arrays are
+ * bit-identical to those packers' for CSR input with strictly ascending rows.
+ *
+ * Protocol: analyze (window column condensation, gives T) -> caller allocates the packed arrays
+ * -> fill.  The scratch buffer carries the analysis between the calls and must not be touched
+ * in between.
+ * ------------------------------------------------------------------------------------------ */
+
+/* Bytes of scratch needed by mask_pack_analyze for a matrix with M rows and nnz entries. */
+size_t mask_pack_scratch_bytes(int32_t M, int64_t nnz);
+
+/* Window column condensation (main_16x8.cu:209-251): writes val_soff[W+1] (exclusive scan of
+ * tiles per window) and returns T through *h_T.  Synchronises the stream. */
+int mask_pack_analyze(const int32_t* d_rowptr, const int32_t* d_colind, int32_t M, int32_t K,
+                      int64_t nnz, void* d_scratch, size_t scratch_bytes, int32_t* d_val_soff,
+                      int64_t* h_T, void* stream);
+
+/* SR-BCRS 16x8 arrays (main_16x8.cu:288-318): val_sidx[8T] (tail slots of a window repeat its
+ * last real column), val_block_val[128T] (tile t, element (r,c) at 128t + Swizzle<2,2,3>(8r+c),
+ * zeros elsewhere).  Optional side outputs of the extension packer
+ * (SRBCRSSpMM_kernel.cu:241,250,268), each may be NULL: block_partition[W] = tiles per window,
+ * edge_to_col[nnz] = condensed position of each entry, edge_to_row[nnz] = its row. */
+int mask_srbcrs_fill(const int32_t* d_rowptr, const int32_t* d_colind, const float* d_values,
+                     int32_t M, int64_t nnz, const void* d_scratch, const int32_t* d_val_soff,
+                     int64_t T, int32_t* d_val_sidx, float* d_val_block_val,
+                     int32_t* d_block_partition, int32_t* d_edge_to_col, int32_t* d_edge_to_row,
+                     void* stream);
+
+/* ME-TCF, step 1 (main.cu:393-453): val_coo_off[2T+1] ([begin, begin+count] per tile, runs
+ * padded to 8, closing entry nnz_pad); returns nnz_pad through *h_nnz_pad.  d_tile_rows is
+ * caller-provided scratch of T 64-bit words, consumed by mask_metcf_fill.  Synchronises. */
+int mask_metcf_offsets(const int32_t* d_rowptr, int32_t M, int64_t nnz, const void* d_scratch,
+                       const int32_t* d_val_soff, int64_t T, int32_t* d_val_coo_off,
+                       uint64_t* d_tile_rows, int64_t* h_nnz_pad, void* stream);
+
+/* ME-TCF, step 2 (main.cu:455-517): val_sidx[8T] (tail slots 0), val_coo_idx[nnz_pad]
+ * (Swizzle<1,2,3>(8r+c)), val_coo_val[nnz_pad]; entries of a tile ordered by row, then CSR
+ * order; padding slots idx 0 / value 0.  d_values may be NULL: every stored entry then gets
+ * the value 1.0f, which is what the reference extension packer writes
+ * (examples/src_fp32/dtc/testbed/DTCSpMM_kernel.cu:450). */
+int mask_metcf_fill(const int32_t* d_rowptr, const int32_t* d_colind, const float* d_values,
+                    int32_t M, int64_t nnz, const void* d_scratch, const int32_t* d_val_soff,
+                    int64_t T, const int32_t* d_val_coo_off, const uint64_t* d_tile_rows,
+                    int64_t nnz_pad, int32_t* d_val_sidx, int32_t* d_val_coo_idx,
+                    float* d_val_coo_val, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Task planners (host, pure functions).  Bit-identical to strict_load_balance
+ * (examples/src_fp32/sr_bcrs/testbed/main_strict_lb_16x8.cu:208-256) and
+ * multi_binding_load_balance (examples/src_fp32/sr_bcrs/testbed/main_multi_bind_16x8.cu:207-271).
+ * Call with NULL output arrays to get the counts, then again with arrays of that size.
+ * ------------------------------------------------------------------------------------------ */
+
+/* Fragments of consecutive tiles such that every group sums to exactly `workload` tiles.
+ * row_block_offset[F+1], row_block_to_window[F], group_offset[G+1]. Returns F via *n_frag. */
+int mask_plan_strict_lb(const int32_t* h_val_soff, int32_t M, int32_t workload,
+                        int32_t* row_block_offset, int32_t* row_block_to_window,
+                        int32_t* group_offset, int64_t* n_frag, int64_t* n_groups);
+
+/* Windows with more than twice the mean tile count are cut into ceil(x/mean) near-equal tasks.
+ * task_window[P], window_split[W], task_soff[P+1]. */
+int mask_plan_multi_bind(const int32_t* h_val_soff, int32_t M, int32_t* task_window,
+                         int32_t* window_split, int32_t* task_soff, int64_t* n_tasks);
+
+/* ------------------------------------------------------------------------------------------
+ * Execution plan: how tiles are dealt to thread blocks.  Replaces the grid mapping of the
+ * reference kernels (one block per window, examples/src_fp32/sr_bcrs/testbed/host_program_16x8.cu:
+ * 157-159; strict_lb / multi_bind tables, host_program_strict_lb.cu:163-289).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct mask_plan mask_plan;
+
+typedef enum mask_policy {
+    MASK_POLICY_AUTO = 0,      /* window-aligned groups; windows larger than a group are split */
+    MASK_POLICY_ROW = 1,       /* one task per window, never split */
+    MASK_POLICY_STRICT_LB = 2, /* the reference's strict_lb tables (exact `group_tiles` per block) */
+    MASK_POLICY_MULTI_BIND = 3 /* the reference's multi_bind tables */
+} mask_policy;
+
+/* Builds a plan from val_soff (device).  group_tiles <= 0 picks a default from T and the SM
+ * count.  Allocates small device arrays owned by the plan; synchronises the stream. */
+int mask_plan_create(const int32_t* d_val_soff, int32_t M, int64_t T, int policy,
+                     int32_t group_tiles, void* stream, mask_plan** out);
+void mask_plan_destroy(mask_plan* plan);
+/* Scratch bytes mask_spmm_* needs with this plan for an N-column product (0 if no window is
+ * split). */
+size_t mask_plan_scratch_bytes(const mask_plan* plan, int32_t N);
+/* Introspection for tests: numbers of fragments, groups, split fragments, and the group size. */
+int mask_plan_info(const mask_plan* plan, int64_t* n_frag, int64_t* n_groups, int64_t* n_partial,
+                   int32_t* group_tiles);
+/* Copies the plan tables to host arrays (frag_offset[F+1], frag_window[F], group_offset[G+1]). */
+int mask_plan_export(const mask_plan* plan, int32_t* frag_offset, int32_t* frag_window,
+                     int32_t* group_offset);
+
+/* ------------------------------------------------------------------------------------------
+ * SpMM.  Replaces sr_bcrs_spmm_kernel_tf32 and its load-balanced variants
+ * (examples/src_fp32/sr_bcrs/testbed/kernel.inc:1590-1700, kernel_lb.inc:62-381) and
+ * dtc_spmm_kernel_fp32_val_idx_bind_stage2 (examples/src_fp32/dtc/testbed/kernel.inc:1982-2134).
+ *
+ * C[M,N] (leading dimension ldc) is fully overwritten -- no zero-fill by the caller and no
+ * atomics: windows split across blocks are summed in tile order from per-fragment partial
+ * tiles in d_scratch, so results are run-to-run deterministic.  B is [K,N] with leading
+ * dimension ldb.  Requirements: N % 4 == 0, ldb % 4 == 0, ldc % 4 == 0, 16-byte aligned B and C.
+ * ------------------------------------------------------------------------------------------ */
+#define MASK_EPILOGUE_NONE 0
+#define MASK_EPILOGUE_RELU 1 /* C = max(A*B, 0), used between GCN layers */
+
+int mask_spmm_srbcrs(const mask_plan* plan, const int32_t* d_val_soff, const int32_t* d_val_sidx,
+                     const float* d_val_block_val, int32_t M, int32_t K, int32_t N,
+                     const float* d_B, int64_t ldb, float* d_C, int64_t ldc, void* d_scratch,
+                     size_t scratch_bytes, int epilogue, void* stream);
+
+int mask_spmm_metcf(const mask_plan* plan, const int32_t* d_val_soff, const int32_t* d_val_sidx,
+                    const int32_t* d_val_coo_off, const int32_t* d_val_coo_idx,
+                    const float* d_val_coo_val, int32_t M, int32_t K, int32_t N, const float* d_B,
+                    int64_t ldb, float* d_C, int64_t ldc, void* d_scratch, size_t scratch_bytes,
+                    int epilogue, void* stream);
+
+/* Development knob for kernel variants, process-wide: "nq" (32-column groups per warp: 1, 2, 4;
+ * 0 = chosen from N) and "min_blocks" (occupancy target of the variant; 0 = default).  Replaces
+ * the reference's tile_b environment switches SRBCRS_TILE_B / DTC_TILE_B
+ * (examples/src_fp32/sr_bcrs/testbed/SRBCRSSpMM_kernel.cu:435-475). */
+int mask_tune(const char* name, int value);
+
+/* ------------------------------------------------------------------------------------------
+ * Host-buffer seam.  Replaces the testbed entry sr_bcrs_test_tf32<16,64,8>
+ * (examples/src_fp32/sr_bcrs/testbed/main_16x8.cu:32-44, host_program_16x8.cu:118-191): packed
+ * arrays, B and C are HOST pointers; the call uploads, runs once and downloads C.  A session
+ * keeps the packed matrix and the plan on the device between calls, like the extension's module
+ * cache (SRBCRSSpMM_kernel.cu:27-45), so a repeated product moves only B and C.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct mask_session mask_session;
+
+int mask_session_create_srbcrs(int32_t M, int32_t K, int64_t T, const int32_t* h_val_soff,
+                               const int32_t* h_val_sidx, const float* h_val_block_val, int policy,
+                               mask_session** out);
+/* From CSR on the host: uploads, packs on the device, plans. */
+int mask_session_create_csr(int32_t M, int32_t K, int64_t nnz, const int32_t* h_rowptr,
+                            const int32_t* h_colind, const float* h_values, int policy,
+                            mask_session** out);
+/* C_host[M,N] = A * B_host[K,N]; pinned host buffers make the copies asynchronous.  kernel_ms,
+ * if not NULL, receives the device time of the SpMM kernels alone. */
+int mask_session_spmm_host(mask_session* s, const float* h_B, float* h_C, int32_t N,
+                           float* kernel_ms);
+int64_t mask_session_tiles(const mask_session* s);
+void mask_session_destroy(mask_session* s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MASK_B200_H_ */

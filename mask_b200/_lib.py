@@ -1,0 +1,77 @@
+"""ctypes binding of ``libmask_b200.so`` (the C ABI declared in ``include/mask_b200.h``).
+
+The library is the only compute path of this package: if it is missing the import fails loudly;
+there is no CPU or PyTorch fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "csrc", "libmask_b200.so")
+
+vp, i32, i64, sz = C.c_void_p, C.c_int32, C.c_int64, C.c_size_t
+
+# name -> (restype, argtypes); every symbol declared in include/mask_b200.h
+SIGNATURES = {
+    "mask_version": (C.c_int, []),
+    "mask_status_string": (C.c_char_p, [C.c_int]),
+    "mask_last_error": (C.c_char_p, []),
+    "mask_pack_scratch_bytes": (sz, [i32, i64]),
+    "mask_pack_analyze": (C.c_int, [vp, vp, i32, i32, i64, vp, sz, vp, C.POINTER(i64), vp]),
+    "mask_srbcrs_fill": (C.c_int, [vp, vp, vp, i32, i64, vp, vp, i64, vp, vp, vp, vp, vp, vp]),
+    "mask_metcf_offsets": (C.c_int, [vp, i32, i64, vp, vp, i64, vp, vp, C.POINTER(i64), vp]),
+    "mask_metcf_fill": (C.c_int, [vp, vp, vp, i32, i64, vp, vp, i64, vp, vp, i64, vp, vp, vp, vp]),
+    "mask_plan_strict_lb": (C.c_int, [vp, i32, i32, vp, vp, vp, C.POINTER(i64), C.POINTER(i64)]),
+    "mask_plan_multi_bind": (C.c_int, [vp, i32, vp, vp, vp, C.POINTER(i64)]),
+    "mask_plan_create": (C.c_int, [vp, i32, i64, C.c_int, i32, vp, C.POINTER(vp)]),
+    "mask_plan_destroy": (None, [vp]),
+    "mask_plan_scratch_bytes": (sz, [vp, i32]),
+    "mask_plan_info": (C.c_int, [vp, C.POINTER(i64), C.POINTER(i64), C.POINTER(i64), C.POINTER(i32)]),
+    "mask_plan_export": (C.c_int, [vp, vp, vp, vp]),
+    "mask_spmm_srbcrs": (C.c_int, [vp, vp, vp, vp, i32, i32, i32, vp, i64, vp, i64, vp, sz, C.c_int, vp]),
+    "mask_spmm_metcf": (C.c_int, [vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, i64, vp, i64, vp, sz, C.c_int, vp]),
+    "mask_tune": (C.c_int, [C.c_char_p, C.c_int]),
+    "mask_session_create_srbcrs": (C.c_int, [i32, i32, i64, vp, vp, vp, C.c_int, C.POINTER(vp)]),
+    "mask_session_create_csr": (C.c_int, [i32, i32, i64, vp, vp, vp, C.c_int, C.POINTER(vp)]),
+    "mask_session_spmm_host": (C.c_int, [vp, vp, vp, i32, C.POINTER(C.c_float)]),
+    "mask_session_tiles": (i64, [vp]),
+    "mask_session_destroy": (None, [vp]),
+}
+
+POLICY = {"auto": 0, "row": 1, "strict_lb": 2, "multi_bind": 3}
+EPILOGUE_NONE, EPILOGUE_RELU = 0, 1
+
+_lib = None
+
+
+class MaskError(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+    def __init__(self, status: int, where: str, detail: str):
+        super().__init__(f"{where}: status {status} ({detail})")
+        self.status = status
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `make -C mask_b200/csrc` "
+                "(or `python -c 'import __graft_entry__ as g; g.build()'`). There is no fallback path.")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)  # AttributeError if the library does not export it
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def check(status: int, where: str) -> None:
+    if status != 0:
+        L = lib()
+        detail = L.mask_last_error().decode() or L.mask_status_string(status).decode()
+        raise MaskError(status, where, detail)

@@ -1,0 +1,196 @@
+// Status reporting and the host-buffer session seam of the C ABI.
+#include <cstdarg>
+#include <cstring>
+
+#include "common.cuh"
+#include "plan.h"
+
+namespace mask {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+}  // namespace mask
+
+extern "C" int mask_version(void) { return 100; }
+
+extern "C" const char* mask_last_error(void) { return mask::g_error; }
+
+extern "C" const char* mask_status_string(int status) {
+    switch (status) {
+        case MASK_OK: return "ok";
+        case MASK_ERR_INVALID_ARGUMENT: return "invalid argument";
+        case MASK_ERR_CUDA: return "CUDA error";
+        case MASK_ERR_UNSORTED_ROWS: return "CSR rows are not strictly ascending";
+        case MASK_ERR_SCRATCH_TOO_SMALL: return "scratch buffer too small";
+        case MASK_ERR_INDEX_OVERFLOW: return "count does not fit the format's int32 indices";
+        case MASK_ERR_COLUMN_RANGE: return "column id out of range";
+        case MASK_ERR_NO_DEVICE: return "no CUDA device";
+        default: return "unknown status";
+    }
+}
+
+// A packed matrix resident on the device plus everything a repeated host-buffer product needs.
+struct mask_session {
+    int32_t M = 0, K = 0;
+    int64_t T = 0;
+    int32_t* d_soff = nullptr;
+    int32_t* d_sidx = nullptr;
+    float* d_blk = nullptr;
+    mask_plan* plan = nullptr;
+    void* d_scratch = nullptr;
+    size_t scratch_bytes = 0;
+    float* d_B = nullptr;
+    float* d_C = nullptr;
+    size_t b_bytes = 0, c_bytes = 0;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+};
+
+namespace mask {
+
+static int session_common_init(mask_session* s) {
+    MASK_CUDA_TRY(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking));
+    MASK_CUDA_TRY(cudaEventCreate(&s->ev0));
+    MASK_CUDA_TRY(cudaEventCreate(&s->ev1));
+    return MASK_OK;
+}
+
+static int grow(void** p, size_t* have, size_t need) {
+    if (need <= *have) return MASK_OK;
+    if (*p) MASK_CUDA_TRY(cudaFree(*p));
+    *p = nullptr;
+    *have = 0;
+    MASK_CUDA_TRY(cudaMalloc(p, need));
+    *have = need;
+    return MASK_OK;
+}
+
+}  // namespace mask
+
+extern "C" void mask_session_destroy(mask_session* s) {
+    if (!s) return;
+    if (s->stream) cudaStreamSynchronize(s->stream);
+    cudaFree(s->d_soff);
+    cudaFree(s->d_sidx);
+    cudaFree(s->d_blk);
+    cudaFree(s->d_scratch);
+    cudaFree(s->d_B);
+    cudaFree(s->d_C);
+    mask_plan_destroy(s->plan);
+    if (s->ev0) cudaEventDestroy(s->ev0);
+    if (s->ev1) cudaEventDestroy(s->ev1);
+    if (s->stream) cudaStreamDestroy(s->stream);
+    delete s;
+}
+
+extern "C" int mask_session_create_srbcrs(int32_t M, int32_t K, int64_t T, const int32_t* h_val_soff,
+                                          const int32_t* h_val_sidx, const float* h_val_block_val, int policy,
+                                          mask_session** out) {
+    using namespace mask;
+    MASK_REQUIRE(out != nullptr, "out is NULL");
+    *out = nullptr;
+    MASK_REQUIRE(M >= 1 && K >= 1 && T >= 0 && h_val_soff, "bad arguments");
+    MASK_REQUIRE(T == 0 || (h_val_sidx && h_val_block_val), "packed arrays are NULL");
+    mask_session* s = new mask_session();
+    s->M = M; s->K = K; s->T = T;
+    const size_t W = (size_t)(M + kWinRows - 1) / kWinRows;
+    auto body = [&]() -> int {
+        int rc = session_common_init(s);
+        if (rc != MASK_OK) return rc;
+        MASK_CUDA_TRY(cudaMalloc((void**)&s->d_soff, (W + 1) * 4));
+        MASK_CUDA_TRY(cudaMalloc((void**)&s->d_sidx, std::max<size_t>((size_t)T * 8 * 4, 4)));
+        MASK_CUDA_TRY(cudaMalloc((void**)&s->d_blk, std::max<size_t>((size_t)T * 128 * 4, 4)));
+        MASK_CUDA_TRY(cudaMemcpyAsync(s->d_soff, h_val_soff, (W + 1) * 4, cudaMemcpyHostToDevice, s->stream));
+        if (T > 0) {
+            MASK_CUDA_TRY(cudaMemcpyAsync(s->d_sidx, h_val_sidx, (size_t)T * 8 * 4, cudaMemcpyHostToDevice, s->stream));
+            MASK_CUDA_TRY(cudaMemcpyAsync(s->d_blk, h_val_block_val, (size_t)T * 128 * 4, cudaMemcpyHostToDevice, s->stream));
+        }
+        return mask_plan_create(s->d_soff, M, T, policy, 0, s->stream, &s->plan);
+    };
+    int rc = body();
+    if (rc != MASK_OK) { mask_session_destroy(s); return rc; }
+    *out = s;
+    return MASK_OK;
+}
+
+extern "C" int mask_session_create_csr(int32_t M, int32_t K, int64_t nnz, const int32_t* h_rowptr,
+                                       const int32_t* h_colind, const float* h_values, int policy,
+                                       mask_session** out) {
+    using namespace mask;
+    MASK_REQUIRE(out != nullptr, "out is NULL");
+    *out = nullptr;
+    MASK_REQUIRE(M >= 1 && K >= 1 && nnz >= 0 && h_rowptr, "bad arguments");
+    MASK_REQUIRE(nnz == 0 || (h_colind && h_values), "colind or values is NULL");
+    mask_session* s = new mask_session();
+    s->M = M; s->K = K;
+    const size_t W = (size_t)(M + kWinRows - 1) / kWinRows;
+    int32_t *d_rowptr = nullptr, *d_colind = nullptr;
+    float* d_values = nullptr;
+    void* d_ws = nullptr;
+    auto body = [&]() -> int {
+        int rc = session_common_init(s);
+        if (rc != MASK_OK) return rc;
+        const size_t n = (size_t)std::max<int64_t>(nnz, 1);
+        MASK_CUDA_TRY(cudaMalloc((void**)&d_rowptr, ((size_t)M + 1) * 4));
+        MASK_CUDA_TRY(cudaMalloc((void**)&d_colind, n * 4));
+        MASK_CUDA_TRY(cudaMalloc((void**)&d_values, n * 4));
+        MASK_CUDA_TRY(cudaMemcpyAsync(d_rowptr, h_rowptr, ((size_t)M + 1) * 4, cudaMemcpyHostToDevice, s->stream));
+        if (nnz > 0) {
+            MASK_CUDA_TRY(cudaMemcpyAsync(d_colind, h_colind, (size_t)nnz * 4, cudaMemcpyHostToDevice, s->stream));
+            MASK_CUDA_TRY(cudaMemcpyAsync(d_values, h_values, (size_t)nnz * 4, cudaMemcpyHostToDevice, s->stream));
+        }
+        const size_t ws = mask_pack_scratch_bytes(M, nnz);
+        MASK_CUDA_TRY(cudaMalloc(&d_ws, ws));
+        MASK_CUDA_TRY(cudaMalloc((void**)&s->d_soff, (W + 1) * 4));
+        rc = mask_pack_analyze(d_rowptr, d_colind, M, K, nnz, d_ws, ws, s->d_soff, &s->T, s->stream);
+        if (rc != MASK_OK) return rc;
+        MASK_CUDA_TRY(cudaMalloc((void**)&s->d_sidx, std::max<size_t>((size_t)s->T * 8 * 4, 4)));
+        MASK_CUDA_TRY(cudaMalloc((void**)&s->d_blk, std::max<size_t>((size_t)s->T * 128 * 4, 4)));
+        rc = mask_srbcrs_fill(d_rowptr, d_colind, d_values, M, nnz, d_ws, s->d_soff, s->T, s->d_sidx, s->d_blk, nullptr,
+                              nullptr, nullptr, s->stream);
+        if (rc != MASK_OK) return rc;
+        return mask_plan_create(s->d_soff, M, s->T, policy, 0, s->stream, &s->plan);
+    };
+    int rc = body();
+    if (s->stream) cudaStreamSynchronize(s->stream);
+    cudaFree(d_rowptr);
+    cudaFree(d_colind);
+    cudaFree(d_values);
+    cudaFree(d_ws);
+    if (rc != MASK_OK) { mask_session_destroy(s); return rc; }
+    *out = s;
+    return MASK_OK;
+}
+
+extern "C" int64_t mask_session_tiles(const mask_session* s) { return s ? s->T : -1; }
+
+extern "C" int mask_session_spmm_host(mask_session* s, const float* h_B, float* h_C, int32_t N, float* kernel_ms) {
+    using namespace mask;
+    MASK_REQUIRE(s != nullptr, "session is NULL");
+    MASK_REQUIRE(N >= 0 && N % 4 == 0, "N must be a non-negative multiple of 4");
+    if (kernel_ms) *kernel_ms = 0.f;
+    if (N == 0) return MASK_OK;
+    MASK_REQUIRE(h_B && h_C, "B or C is NULL");
+    const size_t bb = (size_t)s->K * N * 4, cb = (size_t)s->M * N * 4;
+    int rc = grow((void**)&s->d_B, &s->b_bytes, bb);
+    if (rc == MASK_OK) rc = grow((void**)&s->d_C, &s->c_bytes, cb);
+    if (rc == MASK_OK) rc = grow(&s->d_scratch, &s->scratch_bytes, mask_plan_scratch_bytes(s->plan, N));
+    if (rc != MASK_OK) return rc;
+    MASK_CUDA_TRY(cudaMemcpyAsync(s->d_B, h_B, bb, cudaMemcpyHostToDevice, s->stream));
+    MASK_CUDA_TRY(cudaEventRecord(s->ev0, s->stream));
+    rc = mask_spmm_srbcrs(s->plan, s->d_soff, s->d_sidx, s->d_blk, s->M, s->K, N, s->d_B, N, s->d_C, N, s->d_scratch,
+                          s->scratch_bytes, MASK_EPILOGUE_NONE, s->stream);
+    if (rc != MASK_OK) return rc;
+    MASK_CUDA_TRY(cudaEventRecord(s->ev1, s->stream));
+    MASK_CUDA_TRY(cudaMemcpyAsync(h_C, s->d_C, cb, cudaMemcpyDeviceToHost, s->stream));
+    MASK_CUDA_TRY(cudaStreamSynchronize(s->stream));
+    if (kernel_ms) MASK_CUDA_TRY(cudaEventElapsedTime(kernel_ms, s->ev0, s->ev1));
+    return MASK_OK;
+}

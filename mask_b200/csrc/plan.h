@@ -1,0 +1,31 @@
+// Execution plan: fragments of consecutive tiles, grouped per thread block.
+#pragma once
+
+#include <cstdint>
+#include <vector>
+
+#include "mask_b200.h"
+
+// Fragment f covers tiles [frag_off[f], frag_off[f+1]) of window frag_win[f]; fragments are in
+// window order, so tile ranges are contiguous and windows without tiles appear as empty
+// fragments (their rows of C must still be written).  frag_slot[f] is -1 when the fragment is
+// its whole window (direct store to C) and otherwise the index of its 16xN partial tile in
+// scratch.  Thread block g processes fragments [group_off[g], group_off[g+1]).  head_frag lists
+// the first fragment of every split window for the fix-up pass.
+struct mask_plan {
+    int32_t M = 0;
+    int32_t W = 0;
+    int64_t T = 0;
+    int policy = 0;
+    int32_t group_tiles = 0;
+    int64_t F = 0;  // fragments
+    int64_t G = 0;  // groups (thread blocks)
+    int64_t P = 0;  // fragments that are part of a split window
+    int64_t H = 0;  // split windows
+    std::vector<int32_t> h_frag_off, h_frag_win, h_frag_slot, h_group_off, h_head_frag;
+    int32_t* d_frag_off = nullptr;
+    int32_t* d_frag_win = nullptr;
+    int32_t* d_frag_slot = nullptr;
+    int32_t* d_group_off = nullptr;
+    int32_t* d_head_frag = nullptr;
+};

@@ -1,0 +1,214 @@
+"""Torch-tensor front end of the C ABI: device format builder, execution plans and SpMM.
+
+PyTorch is used for device memory and streams only; every computation happens in
+``libmask_b200.so``.  All tensors are CUDA tensors on the current device.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+
+import torch
+
+from . import _lib
+from ._lib import check, lib
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _req(t, dtype, name):
+    if not (isinstance(t, torch.Tensor) and t.is_cuda):
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    if t.dtype != dtype:
+        raise RuntimeError(f"{name} must be {str(dtype).replace('torch.', '')}")
+
+
+class Plan:
+    """How tiles are dealt to thread blocks (``mask_plan``)."""
+
+    def __init__(self, val_soff: torch.Tensor, M: int, T: int, policy: str = "auto", group_tiles: int = 0):
+        _req(val_soff, torch.int32, "val_soff")
+        h = C.c_void_p()
+        check(lib().mask_plan_create(_ptr(val_soff), M, T, _lib.POLICY[policy], group_tiles, _stream(), C.byref(h)),
+              "mask_plan_create")
+        self._h = h
+        self.policy = policy
+        self.M, self.T = M, T
+        self._scratch = None
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            lib().mask_plan_destroy(h)
+
+    def scratch_bytes(self, N: int) -> int:
+        return int(lib().mask_plan_scratch_bytes(self._h, N))
+
+    def info(self) -> dict:
+        f, g, p, gt = C.c_int64(), C.c_int64(), C.c_int64(), C.c_int32()
+        check(lib().mask_plan_info(self._h, C.byref(f), C.byref(g), C.byref(p), C.byref(gt)), "mask_plan_info")
+        return dict(fragments=f.value, groups=g.value, partial=p.value, group_tiles=gt.value)
+
+    def export(self):
+        """Host copies of (frag_offset[F+1], frag_window[F], group_offset[G+1])."""
+        i = self.info()
+        fo = torch.zeros(i["fragments"] + 1, dtype=torch.int32)
+        fw = torch.zeros(max(i["fragments"], 1), dtype=torch.int32)
+        go = torch.zeros(i["groups"] + 1, dtype=torch.int32)
+        check(lib().mask_plan_export(self._h, _ptr(fo), _ptr(fw), _ptr(go)), "mask_plan_export")
+        return fo, fw[: i["fragments"]], go
+
+    def scratch(self, N: int, device) -> torch.Tensor | None:
+        need = self.scratch_bytes(N)
+        if need == 0:
+            return None
+        if self._scratch is None or self._scratch.numel() < need or self._scratch.device != device:
+            self._scratch = torch.empty(need, dtype=torch.uint8, device=device)
+        return self._scratch
+
+
+@dataclass
+class PackedSRBCRS:
+    """SR-BCRS 16x8: val_soff int32[W+1], val_sidx int32[8T], val_block_val f32[128T]."""
+    M: int
+    K: int
+    T: int
+    nnz: int
+    val_soff: torch.Tensor
+    val_sidx: torch.Tensor
+    val_block_val: torch.Tensor
+    block_partition: torch.Tensor | None = None
+    edge_to_col: torch.Tensor | None = None
+    edge_to_row: torch.Tensor | None = None
+    plans: dict = field(default_factory=dict)
+
+    def plan(self, policy: str = "auto", group_tiles: int = 0) -> Plan:
+        key = (policy, group_tiles)
+        if key not in self.plans:
+            self.plans[key] = Plan(self.val_soff, self.M, self.T, policy, group_tiles)
+        return self.plans[key]
+
+
+@dataclass
+class PackedMETCF:
+    """ME-TCF: val_soff, val_sidx (tail 0), val_coo_off int32[2T+1], val_coo_idx / val_coo_val [nnz_pad]."""
+    M: int
+    K: int
+    T: int
+    nnz: int
+    nnz_pad: int
+    val_soff: torch.Tensor
+    val_sidx: torch.Tensor
+    val_coo_off: torch.Tensor
+    val_coo_idx: torch.Tensor
+    val_coo_val: torch.Tensor
+    plans: dict = field(default_factory=dict)
+
+    plan = PackedSRBCRS.plan
+
+
+def _analyze(rowptr, colind, M, K):
+    _req(rowptr, torch.int32, "rowptr")
+    _req(colind, torch.int32, "colind")
+    if M < 1:
+        raise RuntimeError("num_nodes must be positive")
+    if rowptr.numel() != M + 1:
+        raise RuntimeError("rowptr must have num_nodes + 1 entries")
+    L = lib()
+    nnz = int(colind.numel())
+    dev = rowptr.device
+    W = (M + 15) // 16
+    ws_bytes = int(L.mask_pack_scratch_bytes(M, nnz))
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    val_soff = torch.empty(W + 1, dtype=torch.int32, device=dev)
+    T = C.c_int64(0)
+    check(L.mask_pack_analyze(_ptr(rowptr), _ptr(colind), M, K, nnz, _ptr(ws), ws_bytes, _ptr(val_soff), C.byref(T),
+                              _stream()), "mask_pack_analyze")
+    return ws, val_soff, int(T.value), nnz
+
+
+def pack_srbcrs(rowptr, colind, values, M: int, K: int, side_outputs: bool = False) -> PackedSRBCRS:
+    """CSR (device, rows strictly ascending) -> SR-BCRS 16x8 on the device."""
+    _req(values, torch.float32, "values")
+    if values.numel() != colind.numel():
+        raise RuntimeError("values length must equal colind length")
+    ws, val_soff, T, nnz = _analyze(rowptr, colind, M, K)
+    dev = rowptr.device
+    val_sidx = torch.empty(8 * T, dtype=torch.int32, device=dev)
+    val_block_val = torch.empty(128 * T, dtype=torch.float32, device=dev)
+    bp = e2c = e2r = None
+    if side_outputs:
+        bp = torch.empty((M + 15) // 16, dtype=torch.int32, device=dev)
+        e2c = torch.empty(nnz, dtype=torch.int32, device=dev)
+        e2r = torch.empty(nnz, dtype=torch.int32, device=dev)
+    check(lib().mask_srbcrs_fill(_ptr(rowptr), _ptr(colind), _ptr(values), M, nnz, _ptr(ws), _ptr(val_soff), T,
+                                 _ptr(val_sidx), _ptr(val_block_val), _ptr(bp), _ptr(e2c), _ptr(e2r), _stream()),
+          "mask_srbcrs_fill")
+    return PackedSRBCRS(M, K, T, nnz, val_soff, val_sidx, val_block_val, bp, e2c, e2r)
+
+
+def pack_metcf(rowptr, colind, values, M: int, K: int) -> PackedMETCF:
+    """CSR (device) -> ME-TCF on the device.  ``values=None`` stores 1.0 for every entry."""
+    if values is not None:
+        _req(values, torch.float32, "values")
+    ws, val_soff, T, nnz = _analyze(rowptr, colind, M, K)
+    dev = rowptr.device
+    L = lib()
+    val_coo_off = torch.empty(2 * T + 1, dtype=torch.int32, device=dev)
+    tile_rows = torch.empty(max(T, 1), dtype=torch.int64, device=dev)
+    pad = C.c_int64(0)
+    check(L.mask_metcf_offsets(_ptr(rowptr), M, nnz, _ptr(ws), _ptr(val_soff), T, _ptr(val_coo_off), _ptr(tile_rows),
+                               C.byref(pad), _stream()), "mask_metcf_offsets")
+    nnz_pad = int(pad.value)
+    val_sidx = torch.empty(8 * T, dtype=torch.int32, device=dev)
+    val_coo_idx = torch.empty(nnz_pad, dtype=torch.int32, device=dev)
+    val_coo_val = torch.empty(nnz_pad, dtype=torch.float32, device=dev)
+    check(L.mask_metcf_fill(_ptr(rowptr), _ptr(colind), _ptr(values), M, nnz, _ptr(ws), _ptr(val_soff), T,
+                            _ptr(val_coo_off), _ptr(tile_rows), nnz_pad, _ptr(val_sidx), _ptr(val_coo_idx),
+                            _ptr(val_coo_val), _stream()), "mask_metcf_fill")
+    return PackedMETCF(M, K, T, nnz, nnz_pad, val_soff, val_sidx, val_coo_off, val_coo_idx, val_coo_val)
+
+
+def spmm(packed, dense: torch.Tensor, out: torch.Tensor | None = None, policy: str = "auto", relu: bool = False,
+         plan: Plan | None = None) -> torch.Tensor:
+    """out[M,N] = A @ dense[K,N] on the current stream.  ``out`` is fully overwritten."""
+    _req(dense, torch.float32, "dense")
+    if dense.dim() != 2:
+        raise RuntimeError("dense must be 2-D")
+    if dense.size(0) != packed.K:
+        raise RuntimeError(f"dense has {dense.size(0)} rows, the matrix has {packed.K} columns")
+    N = int(dense.size(1))
+    if out is None:
+        out = torch.empty((packed.M, N), dtype=torch.float32, device=dense.device)
+    else:
+        _req(out, torch.float32, "out")
+        if tuple(out.shape) != (packed.M, N):
+            raise RuntimeError("out has the wrong shape")
+    if N == 0:
+        return out
+    plan = plan or packed.plan(policy)
+    scratch = plan.scratch(N, dense.device)
+    sb = 0 if scratch is None else scratch.numel()
+    epi = _lib.EPILOGUE_RELU if relu else _lib.EPILOGUE_NONE
+    L = lib()
+    if isinstance(packed, PackedMETCF):
+        check(L.mask_spmm_metcf(plan._h, _ptr(packed.val_soff), _ptr(packed.val_sidx), _ptr(packed.val_coo_off),
+                                _ptr(packed.val_coo_idx), _ptr(packed.val_coo_val), packed.M, packed.K, N, _ptr(dense),
+                                N, _ptr(out), N, _ptr(scratch), sb, epi, _stream()), "mask_spmm_metcf")
+    else:
+        check(L.mask_spmm_srbcrs(plan._h, _ptr(packed.val_soff), _ptr(packed.val_sidx), _ptr(packed.val_block_val),
+                                 packed.M, packed.K, N, _ptr(dense), N, _ptr(out), N, _ptr(scratch), sb, epi,
+                                 _stream()), "mask_spmm_srbcrs")
+    return out
+
+
+def tune(name: str, value: int) -> None:
+    check(lib().mask_tune(name.encode(), value), "mask_tune")

@@ -1,0 +1,120 @@
+"""GPU parity: the device format builder against the CPU oracle and the golden fixtures,
+bit for bit, through the C ABI."""
+import numpy as np
+import pytest
+
+from tests import cases
+
+pytestmark = pytest.mark.gpu
+BITS = lambda a: np.ascontiguousarray(a).view(np.int32) if a.dtype == np.float32 else a
+
+
+def _dev(m):
+    import torch
+    return (torch.from_numpy(m.rowptr).cuda(), torch.from_numpy(m.colind).cuda(), torch.from_numpy(m.values).cuda())
+
+
+def _check_srbcrs(p, want, prefix=""):
+    assert p.T == len(want[prefix + "val_sidx"]) // 8
+    for k in ("val_soff", "val_sidx", "val_block_val"):
+        assert np.array_equal(BITS(getattr(p, k).cpu().numpy()), BITS(want[prefix + k])), k
+
+
+def _check_metcf(p, want, prefix=""):
+    assert p.nnz_pad == len(want[prefix + "val_coo_idx"])
+    for k in ("val_soff", "val_sidx", "val_coo_off", "val_coo_idx", "val_coo_val"):
+        assert np.array_equal(BITS(getattr(p, k).cpu().numpy()), BITS(want[prefix + k])), k
+
+
+@pytest.mark.parametrize("name", cases.golden_names())
+def test_pack_matches_golden(name):
+    from mask_b200 import engine
+    m, g = cases.load_golden(name)
+    rp, ci, va = _dev(m)
+    _check_srbcrs(engine.pack_srbcrs(rp, ci, va, m.M, m.K), g, "sr_")
+    _check_metcf(engine.pack_metcf(rp, ci, va, m.M, m.K), g, "me_")
+
+
+@pytest.mark.parametrize("name", sorted(cases.SMALL))
+def test_pack_matches_oracle(oracle_mod, name):
+    from mask_b200 import engine
+    m = cases.SMALL[name]()
+    rp, ci, va = _dev(m)
+    p = engine.pack_srbcrs(rp, ci, va, m.M, m.K, side_outputs=True)
+    _check_srbcrs(p, oracle_mod.pack_srbcrs(m.M, m.rowptr, m.colind, m.values))
+    bp, e2c, e2r = oracle_mod.edge_maps(m.M, m.rowptr, m.colind)
+    assert np.array_equal(p.block_partition.cpu().numpy(), bp)
+    assert np.array_equal(p.edge_to_col.cpu().numpy(), e2c)
+    assert np.array_equal(p.edge_to_row.cpu().numpy(), e2r)
+    _check_metcf(engine.pack_metcf(rp, ci, va, m.M, m.K), oracle_mod.pack_metcf(m.M, m.rowptr, m.colind, m.values))
+
+
+def test_pack_metcf_unit_values(oracle_mod):
+    """values=None stores 1.0 for every entry, as the reference extension packer does."""
+    from mask_b200 import engine
+    m = cases.SMALL["rmat10"]()
+    rp, ci, _ = _dev(m)
+    p = engine.pack_metcf(rp, ci, None, m.M, m.K)
+    _check_metcf(p, oracle_mod.pack_metcf(m.M, m.rowptr, m.colind, np.ones_like(m.values)))
+
+
+@pytest.mark.parametrize("workload,kw", [("rmat20_gcn", dict(scale=16)), ("stencil27_100", dict(grid=40)),
+                                         ("rmat22_sym", dict(scale=15))])
+def test_pack_medium_matches_oracle(oracle_mod, workload, kw):
+    """Medium sizes (hub windows with tens of thousands of entries, scans spanning many chunks)."""
+    from mask_b200 import engine, generators as G
+    m, _ = G.make_workload(workload, **kw)
+    rp, ci, va = _dev(m)
+    _check_srbcrs(engine.pack_srbcrs(rp, ci, va, m.M, m.K), oracle_mod.pack_srbcrs(m.M, m.rowptr, m.colind, m.values))
+    _check_metcf(engine.pack_metcf(rp, ci, va, m.M, m.K), oracle_mod.pack_metcf(m.M, m.rowptr, m.colind, m.values))
+
+
+def test_pack_rejects_bad_input():
+    import torch
+    from mask_b200 import engine, _lib
+    m = cases.SMALL["uniform512"]()
+    rp, ci, va = _dev(m)
+    bad = ci.clone()
+    s = int(m.rowptr[5])
+    bad[s], bad[s + 1] = ci[s + 1], ci[s]  # row 5 no longer ascending
+    with pytest.raises(_lib.MaskError) as e:
+        engine.pack_srbcrs(rp, bad, va, m.M, m.K)
+    assert e.value.status == 3
+    oob = ci.clone()
+    oob[0] = m.K
+    with pytest.raises(_lib.MaskError) as e:
+        engine.pack_srbcrs(rp, oob, va, m.M, m.K)
+    assert e.value.status == 6
+    with pytest.raises(RuntimeError):
+        engine.pack_srbcrs(rp, ci.to(torch.int64), va, m.M, m.K)
+    with pytest.raises(RuntimeError):
+        engine.pack_srbcrs(rp.cpu(), ci, va, m.M, m.K)
+    # the context is still healthy
+    assert engine.pack_srbcrs(rp, ci, va, m.M, m.K).T > 0
+
+
+def test_plan_tables(oracle_mod):
+    """Plans cover every tile exactly once, in order, and the strict_lb policy reproduces the
+    reference tables (plus empty fragments for windows without tiles)."""
+    from mask_b200 import engine
+    for name in ("m33_empty_window", "hub_rows", "rmat10", "all_empty"):
+        m = cases.SMALL[name]()
+        rp, ci, va = _dev(m)
+        p = engine.pack_srbcrs(rp, ci, va, m.M, m.K)
+        soff = p.val_soff.cpu().numpy()
+        W = (m.M + 15) // 16
+        for policy, gt in (("auto", 0), ("auto", 4), ("row", 0), ("strict_lb", 8), ("multi_bind", 0)):
+            plan = engine.Plan(p.val_soff, m.M, p.T, policy, gt)
+            fo, fw, go = (x.numpy() for x in plan.export())
+            info = plan.info()
+            assert fo[0] == 0 and fo[-1] == p.T and np.all(np.diff(fo) >= 0)
+            assert go[0] == 0 and go[-1] == info["fragments"] and np.all(np.diff(go) > 0)
+            assert np.all(np.diff(fw) >= 0) and set(fw.tolist()) == set(range(W))  # every window is written
+            for f in range(info["fragments"]):
+                assert soff[fw[f]] <= fo[f] and fo[f + 1] <= soff[fw[f] + 1]
+            if policy == "row":
+                assert info["partial"] == 0 and info["groups"] == W
+            if policy == "strict_lb":
+                rbo, rb2w, _ = oracle_mod.strict_lb_plan(m.M, soff, 8)
+                keep = np.diff(fo) > 0
+                assert np.array_equal(fo[:-1][keep], rbo[:-1]) and np.array_equal(fw[keep], rb2w)

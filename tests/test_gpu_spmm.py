@@ -1,0 +1,207 @@
+"""GPU parity: the SpMM kernels against the host FP32 reference SpMM of the oracle, through the
+C ABI.  Tolerance (stated by the task): |C - Cref|_ij <= 2e-3 * (|A|.|B|)_ij + 1e-6."""
+import numpy as np
+import pytest
+
+from tests import cases
+
+pytestmark = pytest.mark.gpu
+RTOL, ATOL = 2e-3, 1e-6
+
+
+def _dev(m):
+    import torch
+    return (torch.from_numpy(m.rowptr).cuda(), torch.from_numpy(m.colind).cuda(), torch.from_numpy(m.values).cuda())
+
+
+def _dense(K, N, seed):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    return rng.standard_normal((K, N), dtype=np.float32)
+
+
+def _assert_close(oracle_mod, m, B, got, relu=False):
+    ref = oracle_mod.spmm_f32(m.M, m.rowptr, m.colind, m.values, B)
+    absp = oracle_mod.spmm_abs_f64(m.M, m.rowptr, m.colind, m.values, B)
+    if relu:
+        # max(x,0) is 1-Lipschitz, so the same bound holds after the activation
+        ref = np.maximum(ref, 0)
+    bad, worst = oracle_mod.check_tolerance(got, ref, absp, RTOL, ATOL)
+    assert bad == 0, f"{bad} elements outside tolerance, worst ratio {worst}"
+    return worst
+
+
+@pytest.mark.parametrize("name", sorted(cases.SMALL))
+@pytest.mark.parametrize("N", [64, 512])
+def test_srbcrs_spmm_matches_oracle(oracle_mod, name, N):
+    import torch
+    from mask_b200 import engine
+    m = cases.SMALL[name]()
+    rp, ci, va = _dev(m)
+    p = engine.pack_srbcrs(rp, ci, va, m.M, m.K)
+    B = _dense(m.K, N, 17)
+    out = torch.full((m.M, N), float("nan"), device="cuda")  # every element must be overwritten
+    engine.spmm(p, torch.from_numpy(B).cuda(), out=out)
+    _assert_close(oracle_mod, m, B, out.cpu().numpy())
+
+
+@pytest.mark.parametrize("N", [4, 16, 36, 100, 128, 160, 256, 320, 1024])
+def test_srbcrs_spmm_column_counts(oracle_mod, N):
+    import torch
+    from mask_b200 import engine
+    m = cases.SMALL["three_four_tiles"]()
+    rp, ci, va = _dev(m)
+    p = engine.pack_srbcrs(rp, ci, va, m.M, m.K)
+    B = _dense(m.K, N, N)
+    out = torch.full((m.M, N), float("nan"), device="cuda")
+    engine.spmm(p, torch.from_numpy(B).cuda(), out=out)
+    _assert_close(oracle_mod, m, B, out.cpu().numpy())
+
+
+@pytest.mark.parametrize("policy,gt", [("auto", 0), ("auto", 2), ("row", 0), ("strict_lb", 0), ("strict_lb", 3),
+                                       ("multi_bind", 0)])
+@pytest.mark.parametrize("name", ["hub_rows", "rmat10", "m33_empty_window", "all_empty", "m17"])
+def test_srbcrs_spmm_policies(oracle_mod, name, policy, gt):
+    """Every task mapping (including windows split over several blocks and summed from scratch)
+    gives the same product; split-window results are deterministic."""
+    import torch
+    from mask_b200 import engine
+    m = cases.SMALL[name]()
+    rp, ci, va = _dev(m)
+    p = engine.pack_srbcrs(rp, ci, va, m.M, m.K)
+    N = 96
+    B = _dense(m.K, N, 5)
+    Bd = torch.from_numpy(B).cuda()
+    plan = engine.Plan(p.val_soff, m.M, p.T, policy, gt)
+    out1 = torch.full((m.M, N), float("nan"), device="cuda")
+    engine.spmm(p, Bd, out=out1, plan=plan)
+    _assert_close(oracle_mod, m, B, out1.cpu().numpy())
+    out2 = torch.full((m.M, N), float("nan"), device="cuda")
+    engine.spmm(p, Bd, out=out2, plan=plan)
+    assert torch.equal(out1, out2)
+
+
+@pytest.mark.parametrize("nq,mb", [(1, 0), (2, 0), (2, 4), (4, 0), (4, 3)])
+def test_srbcrs_spmm_kernel_variants(oracle_mod, nq, mb):
+    import torch
+    from mask_b200 import engine
+    m = cases.SMALL["rmat12u"]()
+    rp, ci, va = _dev(m)
+    p = engine.pack_srbcrs(rp, ci, va, m.M, m.K)
+    B = _dense(m.K, 512, 9)
+    try:
+        engine.tune("nq", nq)
+        engine.tune("min_blocks", mb)
+        out = engine.spmm(p, torch.from_numpy(B).cuda())
+    finally:
+        engine.tune("nq", 0)
+        engine.tune("min_blocks", 0)
+    _assert_close(oracle_mod, m, B, out.cpu().numpy())
+
+
+@pytest.mark.parametrize("name", ["m1", "m17", "m33_empty_window", "hub_rows", "rmat10", "stencil8", "all_empty"])
+@pytest.mark.parametrize("N", [32, 512])
+def test_metcf_spmm_matches_oracle(oracle_mod, name, N):
+    import torch
+    from mask_b200 import engine
+    m = cases.SMALL[name]()
+    rp, ci, va = _dev(m)
+    p = engine.pack_metcf(rp, ci, va, m.M, m.K)
+    B = _dense(m.K, N, 23)
+    out = torch.full((m.M, N), float("nan"), device="cuda")
+    engine.spmm(p, torch.from_numpy(B).cuda(), out=out, policy="auto")
+    _assert_close(oracle_mod, m, B, out.cpu().numpy())
+    # a dense tile with more than 32 entries exercises the long-run path
+    out2 = engine.spmm(p, torch.from_numpy(B).cuda(), plan=engine.Plan(p.val_soff, m.M, p.T, "auto", 2))
+    _assert_close(oracle_mod, m, B, out2.cpu().numpy())
+
+
+def test_relu_epilogue(oracle_mod):
+    import torch
+    from mask_b200 import engine
+    m = cases.SMALL["hub_rows"]()
+    rp, ci, va = _dev(m)
+    p = engine.pack_srbcrs(rp, ci, va, m.M, m.K)
+    B = _dense(m.K, 64, 2)
+    for gt in (0, 2):  # direct stores and the split-window fix-up path
+        out = engine.spmm(p, torch.from_numpy(B).cuda(), relu=True, plan=engine.Plan(p.val_soff, m.M, p.T, "auto", gt))
+        assert float(out.min()) >= 0.0
+        _assert_close(oracle_mod, m, B, out.cpu().numpy(), relu=True)
+
+
+def test_linearity_and_golden_product(oracle_mod):
+    """Size-independent properties: A(x+y) = Ax + Ay within tolerance; golden fixtures multiply
+    to the oracle product."""
+    import torch
+    from mask_b200 import engine
+    for name in cases.golden_names():
+        m, g = cases.load_golden(name)
+        rp, ci, va = _dev(m)
+        p = engine.pack_srbcrs(rp, ci, va, m.M, m.K)
+        B = _dense(m.K, 48, 31)
+        out = engine.spmm(p, torch.from_numpy(B).cuda())
+        _assert_close(oracle_mod, m, B, out.cpu().numpy())
+    m = cases.SMALL["rmat12u"]()
+    rp, ci, va = _dev(m)
+    p = engine.pack_srbcrs(rp, ci, va, m.M, m.K)
+    X, Y = torch.from_numpy(_dense(m.K, 128, 1)).cuda(), torch.from_numpy(_dense(m.K, 128, 2)).cuda()
+    lhs = engine.spmm(p, X + Y).cpu().numpy()
+    rhs = (engine.spmm(p, X) + engine.spmm(p, Y)).cpu().numpy()
+    absp = oracle_mod.spmm_abs_f64(m.M, m.rowptr, m.colind, m.values, (X.abs() + Y.abs()).cpu().numpy())
+    bad, worst = oracle_mod.check_tolerance(lhs, rhs, absp, 2 * RTOL, ATOL)
+    assert bad == 0, worst
+
+
+def test_spmm_argument_errors():
+    import torch
+    from mask_b200 import engine, _lib
+    m = cases.SMALL["m17"]()
+    rp, ci, va = _dev(m)
+    p = engine.pack_srbcrs(rp, ci, va, m.M, m.K)
+    with pytest.raises(RuntimeError):
+        engine.spmm(p, torch.zeros((m.K + 1, 16), device="cuda"))
+    with pytest.raises(RuntimeError):
+        engine.spmm(p, torch.zeros((m.K, 16), device="cuda", dtype=torch.float64))
+    with pytest.raises(_lib.MaskError):
+        engine.spmm(p, torch.zeros((m.K, 18), device="cuda"))  # N % 4 != 0
+    assert engine.spmm(p, torch.zeros((m.K, 0), device="cuda")).shape == (m.M, 0)
+
+
+def test_session_host_buffers(oracle_mod):
+    """The host-buffer seam: packed arrays, B and C all on the host."""
+    import ctypes as C
+    from mask_b200 import _lib
+    L = _lib.lib()
+    m = cases.SMALL["rmat10"]()
+    sr = oracle_mod.pack_srbcrs(m.M, m.rowptr, m.colind, m.values)
+    B = _dense(m.K, 64, 3)
+    for make in ("packed", "csr"):
+        h = C.c_void_p()
+        if make == "packed":
+            _lib.check(L.mask_session_create_srbcrs(m.M, m.K, sr["T"], sr["val_soff"].ctypes.data, sr["val_sidx"].ctypes.data,
+                                                    sr["val_block_val"].ctypes.data, 0, C.byref(h)), "create")
+        else:
+            _lib.check(L.mask_session_create_csr(m.M, m.K, m.nnz, m.rowptr.ctypes.data, m.colind.ctypes.data,
+                                                 m.values.ctypes.data, 0, C.byref(h)), "create")
+        assert L.mask_session_tiles(h) == sr["T"]
+        out = np.full((m.M, 64), np.nan, dtype=np.float32)
+        ms = C.c_float()
+        _lib.check(L.mask_session_spmm_host(h, B.ctypes.data, out.ctypes.data, 64, C.byref(ms)), "spmm_host")
+        L.mask_session_destroy(h)
+        assert ms.value > 0
+        _assert_close(oracle_mod, m, B, out)
+
+
+def test_medium_rmat_against_oracle(oracle_mod):
+    """A 2^16-node power-law graph at N=512: thousands of groups, split hub windows."""
+    import torch
+    from mask_b200 import engine, generators as G
+    m, bseed = G.make_workload("rmat20_gcn", scale=16)
+    rp, ci, va = _dev(m)
+    p = engine.pack_srbcrs(rp, ci, va, m.M, m.K)
+    B = G.dense_normal(m.K, 512, bseed)
+    out = engine.spmm(p, torch.from_numpy(B).cuda())
+    assert p.plan("auto").info()["partial"] > 0
+    _assert_close(oracle_mod, m, B, out.cpu().numpy())
+    pm = engine.pack_metcf(rp, ci, va, m.M, m.K)
+    out2 = engine.spmm(pm, torch.from_numpy(B).cuda())
+    _assert_close(oracle_mod, m, B, out2.cpu().numpy())
