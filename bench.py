@@ -1,0 +1,373 @@
+#!/usr/bin/env python
+"""SpMM benchmark: effective GFLOP/s (2*nnz*N/t) at N=512 on 1/2/4/8 B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+A step is one product C = A*B over the whole matrix.  The default workload is the symmetric
+power-law graph with 2^20 nodes (GCN-normalised values) packed as SR-BCRS 16x8, B 2^20 x 512
+FP32 N(0,1); synthetic, seeded (the reference project's evaluation matrices are not distributed
+with it).  With N > 1 ranks (torchrun) the rows of A are cut into nnz-balanced panels on window
+boundaries, B is replicated, every rank multiplies its panel and no collective is on the data
+path (strong scaling: the total work is fixed).
+
+One JSON line is printed by rank 0:
+  value      device-side throughput, inputs resident in HBM, CUDA events on the launch stream,
+             max over ranks
+  e2e        the same product through the host-buffer C-ABI call (pinned host B in, host C out,
+             copies inside the timed region)
+  roofline   algorithmic bytes per launch / measured kernel time, against the measured HBM peak
+  cpu_baseline  the host FP32 reference SpMM (CPU port of the reference's cpu_spmm) timed on this
+             box's cores on the same matrix (rank 0, N=1 only); also used to verify the GPU result
+--impl reference times that CPU implementation alone, with all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "SpMM effective GFLOP/s (2*nnz*N/t) at N=512"
+UNIT = "GFLOP/s"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def log(*a):
+    print(*a, file=sys.stderr, flush=True)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.002):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        self.period = period_s
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception as e:  # NVML missing: report clocks as unknown rather than fail the bench
+            self.nv = None
+            log(f"[bench] NVML unavailable: {e}")
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+            getattr(nv, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80): "hw_power_brake",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def build_workload(name: str, scale: int | None):
+    from mask_b200 import generators as G
+    kw = {}
+    if scale is not None:
+        kw = {"grid": scale} if name.startswith("stencil") else ({"n": scale} if name.startswith("uniform") else {"scale": scale})
+    t0 = time.time()
+    m, bseed = G.make_workload(name, **kw)
+    log(f"[bench] workload {name} {kw}: M={m.M} nnz={m.nnz} built in {time.time() - t0:.1f}s")
+    return m, bseed
+
+
+def panel_bounds(m, parts: int, dev) -> list[int]:
+    """Row panel boundaries on 16-row window boundaries.  Panels are balanced by 16x8 tile count
+    (the kernel's cost unit; equal to balanced nnz up to tile fill): every rank runs the cheap
+    window analysis of the device format builder on the whole matrix to get tiles per window."""
+    if parts == 1:
+        return [0, m.M]
+    import torch
+    from mask_b200 import engine
+    from mask_b200.sharding import balanced_panels
+    rp = torch.from_numpy(m.rowptr).to(dev)
+    ci = torch.from_numpy(m.colind).to(dev)
+    _, val_soff, _, _ = engine._analyze(rp, ci, m.M, m.K)
+    return balanced_panels(val_soff.cpu().numpy(), m.M, parts)
+
+
+def algorithmic_bytes(T: int, W: int, M: int, N: int, distinct_cols: int) -> int:
+    """A values + column metadata + every touched row of B once + C written once."""
+    return 4 * 128 * T + 4 * (8 * T + W + 1) + 4 * N * distinct_cols + 4 * M * N
+
+
+def run_reference(args):
+    """CPU arm: the host FP32 reference SpMM with every host thread, on the same workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    from mask_b200 import generators as G
+    m, bseed = build_workload(args.workload, args.scale)
+    N = args.n
+    B = G.dense_normal(m.K, N, bseed)
+    threads = oracle.max_threads()
+    L = oracle.lib()
+    Cm = np.zeros((m.M, N), dtype=np.float32)
+
+    def run(r0, r1):
+        t0 = time.perf_counter()
+        L.oracle_spmm_f32(r0, r1, N, m.rowptr, m.colind, m.values, B, N, Cm, N, threads)
+        return time.perf_counter() - t0
+
+    # size the per-step sample so the whole run stays within about two minutes
+    probe_rows = min(m.M, max(16, m.M // 64))
+    tp = run(0, probe_rows)
+    est_full = tp * m.nnz / max(1, int(m.rowptr[probe_rows]))
+    budget = 120.0 / (args.steps + args.warmup)
+    frac = min(1.0, budget / max(est_full, 1e-9))
+    rows = m.M if frac >= 1.0 else max(16, int(m.M * frac) // 16 * 16)
+    nnz_s = int(m.rowptr[rows])
+    for _ in range(args.warmup):
+        run(0, rows)
+    t = 0.0
+    for _ in range(args.steps):
+        t += run(0, rows)
+    ms = t / args.steps * 1e3
+    val = 2.0 * nnz_s * N / (ms * 1e-3) / 1e9
+    sample = f"rows [0,{rows}) of {m.M} ({nnz_s} of {m.nnz} stored entries) per step"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "M": m.M, "K": m.K, "nnz": m.nnz, "N": N},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="mask_b200", choices=["mask_b200", "reference"])
+    ap.add_argument("--workload", default="rmat20_gcn")
+    ap.add_argument("--scale", type=int, default=None, help="shrink the workload (R-MAT scale / grid / n)")
+    ap.add_argument("--n", type=int, default=512, help="columns of B")
+    ap.add_argument("--format", default="srbcrs", choices=["srbcrs", "metcf"])
+    ap.add_argument("--policy", default="auto")
+    ap.add_argument("--group-tiles", type=int, default=0)
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / verification leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    from mask_b200 import _lib, engine, generators as G
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    N = args.n
+
+    m, bseed = build_workload(args.workload, args.scale)
+    dev = torch.device("cuda", local)
+    bounds = panel_bounds(m, world, dev)
+    r0, r1 = bounds[rank], bounds[rank + 1]
+    panel = m.row_slice(r0, r1) if world > 1 else m
+    Bh = G.dense_normal(m.K, N, bseed)
+    Bd = torch.from_numpy(Bh).to(dev)
+    rp, ci, va = (torch.from_numpy(np.ascontiguousarray(x)).to(dev) for x in (panel.rowptr, panel.colind, panel.values))
+
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    packed = engine.pack_srbcrs(rp, ci, va, panel.M, panel.K) if args.format == "srbcrs" else \
+        engine.pack_metcf(rp, ci, va, panel.M, panel.K)
+    torch.cuda.synchronize()
+    pack_ms = (time.perf_counter() - t0) * 1e3
+    plan = engine.Plan(packed.val_soff, panel.M, packed.T, args.policy, args.group_tiles)
+    info = plan.info()
+    out = torch.empty((panel.M, N), dtype=torch.float32, device=dev)
+    launches_per_step = 1 + (1 if info["partial"] > 0 else 0)
+    log(f"[bench] rank {rank}: rows [{r0},{r1}) nnz={panel.nnz} T={packed.T} pack {pack_ms:.1f} ms plan {info}")
+
+    def step():
+        engine.spmm(packed, Bd, out=out, plan=plan)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    with ClockSampler(local) as clocks:
+        ev[0].record()
+        for i in range(args.steps):
+            step()
+            ev[i + 1].record()
+        torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    per_launch = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = float(t.item()) / args.steps
+    value = 2.0 * m.nnz * N / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end through the host-buffer C ABI (rank-local panel; pinned host buffers) ----
+    L = _lib.lib()
+    e2e = None
+    try:
+        hB = torch.from_numpy(Bh).pin_memory()
+        hC = torch.empty((panel.M, N), dtype=torch.float32).pin_memory()
+        sess = C.c_void_p()
+        sr_host = {k: getattr(packed, k).cpu().numpy() for k in ("val_soff", "val_sidx", "val_block_val")} \
+            if args.format == "srbcrs" else None
+        if sr_host is not None:
+            _lib.check(L.mask_session_create_srbcrs(panel.M, panel.K, packed.T, sr_host["val_soff"].ctypes.data,
+                                                    sr_host["val_sidx"].ctypes.data, sr_host["val_block_val"].ctypes.data,
+                                                    _lib.POLICY[args.policy], C.byref(sess)), "mask_session_create_srbcrs")
+            kms = C.c_float()
+            for _ in range(2):
+                _lib.check(L.mask_session_spmm_host(sess, hB.data_ptr(), hC.data_ptr(), N, C.byref(kms)), "spmm_host")
+            if world > 1:
+                dist.barrier()
+            t0 = time.perf_counter()
+            for _ in range(args.e2e_steps):
+                _lib.check(L.mask_session_spmm_host(sess, hB.data_ptr(), hC.data_ptr(), N, C.byref(kms)), "spmm_host")
+            e2e_ms = (time.perf_counter() - t0) * 1e3 / args.e2e_steps
+            L.mask_session_destroy(sess)
+            te = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(te, op=dist.ReduceOp.MAX)
+            e2e_ms = float(te.item())
+            e2e = {"value": 2.0 * m.nnz * N / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
+                   "h2d_bytes_per_step": int(m.K) * N * 4, "d2h_bytes_per_step": int(panel.M) * N * 4,
+                   "ms_per_step": e2e_ms, "steps": args.e2e_steps,
+                   "api": "mask_session_spmm_host (C ABI, pinned host B in, host C out)"}
+            host_result = hC.numpy()
+        del hB
+    except Exception as e:  # the headline device number must still be printed
+        log(f"[bench] e2e leg failed: {e}")
+        host_result = None
+
+    # ---- roofline of the dominant kernel (rank-local) ----
+    hbm_gbs, peak_src = measured_peaks()
+    W = (panel.M + 15) // 16
+    distinct = int(np.unique(panel.colind).size)
+    G_rows = int(packed.T) * 8  # upper bound of rows fetched without inter-window reuse (incl. padding)
+    bytes_alg = algorithmic_bytes(packed.T, W, panel.M, N, distinct) if args.format == "srbcrs" else \
+        8 * packed.nnz_pad + 4 * (2 * packed.T + 1) + 4 * (8 * packed.T + W + 1) + 4 * N * distinct + 4 * panel.M * N
+    kernel_ms = float(np.mean(per_launch))
+    achieved = bytes_alg / (kernel_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
+                "traffic": None, "peak_source": peak_src, "bytes_algorithmic": bytes_alg,
+                "kernel_ms": kernel_ms, "kernel": "spmm_mma_kernel (+ spmm_fixup_kernel)",
+                "bytes_gather_no_reuse": bytes_alg - 4 * N * distinct + 4 * N * G_rows,
+                "padded_tile_tflop": 256.0 * packed.T * N / 1e12}
+
+    # ---- CPU baseline + verification (rank 0, single GPU only) ----
+    cpu = None
+    verified = None
+    if world == 1 and not args.no_cpu:
+        import oracle
+        threads = oracle.max_threads()
+        Lo = oracle.lib()
+        Cref = np.zeros((m.M, N), dtype=np.float32)
+        t0 = time.perf_counter()
+        Lo.oracle_spmm_f32(0, m.M, N, m.rowptr, m.colind, m.values, Bh, N, Cref, N, threads)
+        cpu_s = time.perf_counter() - t0
+        cpu = {"value": 2.0 * m.nnz * N / cpu_s / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": f"the whole workload once ({m.nnz} stored entries, N={N}), {cpu_s:.2f} s"}
+        got = out.cpu().numpy()
+        rng = np.random.Generator(np.random.PCG64(7))
+        heavy = np.argsort(np.diff(packed.val_soff.cpu().numpy()))[-64:]
+        rows = np.unique(np.concatenate([rng.integers(0, m.M, size=16384),
+                                         (heavy[:, None] * 16 + np.arange(16)[None, :]).ravel()]))
+        rows = rows[rows < m.M]
+        sub_ptr = np.zeros(rows.size + 1, dtype=np.int64)
+        sub_ptr[1:] = np.cumsum(m.rowptr[rows + 1] - m.rowptr[rows])
+        idx = np.concatenate([np.arange(m.rowptr[r], m.rowptr[r + 1]) for r in rows]) if rows.size else np.zeros(0, np.int64)
+        absp = oracle.spmm_abs_f64(rows.size, sub_ptr.astype(np.int32), m.colind[idx], m.values[idx], Bh)
+        bad, worst = oracle.check_tolerance(got[rows], Cref[rows], absp)
+        verified = {"rows_checked": int(rows.size), "violations": bad, "worst_ratio": worst,
+                    "tolerance": "|C-Cref| <= 2e-3*(|A|.|B|) + 1e-6"}
+        if host_result is not None:
+            bad2, worst2 = oracle.check_tolerance(host_result[rows], Cref[rows], absp)
+            verified["e2e_violations"] = bad2
+        if bad:
+            log(f"[bench] VERIFICATION FAILED: {bad} elements outside tolerance")
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "tf32", "data": "synthetic",
+            "config": {"workload": args.workload + (f" scale={args.scale}" if args.scale else ""), "M": m.M, "K": m.K,
+                       "nnz": m.nnz, "N": N, "format": "SR-BCRS 16x8" if args.format == "srbcrs" else "ME-TCF",
+                       "tiles_rank0": packed.T, "policy": args.policy, "plan": info, "pack_ms_rank0": pack_ms,
+                       "partition": "tile-balanced row panels on window boundaries, B replicated" if world > 1 else "none",
+                       "l2": "no flush needed: B and C (M*N*4 bytes each) are far larger than the 126 MB L2"},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks.summary(), "verified": verified,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

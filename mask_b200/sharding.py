@@ -1,0 +1,50 @@
+"""Row-panel partitioning of A for multi-GPU SpMM.
+
+Output rows are independent, so with the dense operand replicated a product needs no exchange:
+rank p multiplies rows [b_p, b_{p+1}) and keeps that panel of C.  Panels start on 16-row window
+boundaries (so every rank packs whole windows and the concatenation of the per-rank formats'
+windows is the single-GPU window sequence) and are cut where the running count of stored entries
+crosses equal shares.  The reference project is single-GPU; this module is new.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+WIN = 16
+
+
+def balanced_panels(win_prefix: np.ndarray, M: int, parts: int) -> list[int]:
+    """Boundaries b_0=0 <= b_1 <= ... <= b_parts=M, each a multiple of 16 (except M), cutting the
+    per-window cost whose exclusive prefix sum is ``win_prefix`` (W+1 entries) into equal shares.
+    With val_soff as the prefix the panels hold equal numbers of 16x8 tiles, which is what the
+    SpMM kernel's time follows."""
+    W = (M + WIN - 1) // WIN
+    assert parts >= 1 and win_prefix.shape[0] == W + 1
+    win_rows = np.minimum(np.arange(W + 1, dtype=np.int64) * WIN, M)
+    win_nnz = np.asarray(win_prefix).astype(np.int64)
+    nnz = int(win_nnz[W])
+    bounds = [0]
+    for p in range(1, parts):
+        target = (nnz * p) // parts
+        w = int(np.searchsorted(win_nnz, target, side="left"))
+        # the boundary whose prefix is closest to the target
+        if w > 0 and w <= W and abs(int(win_nnz[w - 1]) - target) < abs(int(win_nnz[min(w, W)]) - target):
+            w -= 1
+        w = min(max(w, bounds[-1] // WIN if bounds[-1] % WIN == 0 else W), W)
+        bounds.append(int(win_rows[w]))
+    bounds.append(M)
+    for a, b in zip(bounds, bounds[1:]):
+        assert a <= b
+    return bounds
+
+
+def nnz_balanced_panels(rowptr: np.ndarray, M: int, parts: int) -> list[int]:
+    """Panels holding equal numbers of stored entries."""
+    assert rowptr.shape[0] == M + 1
+    W = (M + WIN - 1) // WIN
+    win_rows = np.minimum(np.arange(W + 1, dtype=np.int64) * WIN, M)
+    return balanced_panels(rowptr[win_rows], M, parts)
+
+
+def panel_of(bounds: list[int], rank: int) -> tuple[int, int]:
+    return bounds[rank], bounds[rank + 1]
