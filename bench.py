@@ -201,7 +201,11 @@ def main():
     ap.add_argument("--format", default="srbcrs", choices=["srbcrs", "metcf"])
     ap.add_argument("--policy", default="auto")
     ap.add_argument("--group-tiles", type=int, default=0)
-    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--e2e-steps", type=int, default=3, help="0 skips the host-buffer leg")
+    ap.add_argument("--nq", type=int, default=0, help="kernel variant: 32-column groups per warp (0 = default)")
+    ap.add_argument("--min-blocks", type=int, default=0, help="kernel variant: occupancy target (0 = default)")
+    ap.add_argument("--stages", type=int, default=0, help="kernel variant: ring slots per warp (0 = default)")
+    ap.add_argument("--no-async", action="store_true", help="use the register-pipelined kernel")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / verification leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
@@ -219,6 +223,10 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     N = args.n
+    engine.tune("nq", args.nq)
+    engine.tune("min_blocks", args.min_blocks)
+    engine.tune("stages", args.stages)
+    engine.tune("async", 0 if args.no_async else 1)
 
     m, bseed = build_workload(args.workload, args.scale)
     dev = torch.device("cuda", local)
@@ -270,7 +278,10 @@ def main():
     # ---- end to end through the host-buffer C ABI (rank-local panel; pinned host buffers) ----
     L = _lib.lib()
     e2e = None
+    host_result = None
     try:
+        if args.e2e_steps <= 0:
+            raise RuntimeError("skipped (--e2e-steps 0)")
         hB = torch.from_numpy(Bh).pin_memory()
         hC = torch.empty((panel.M, N), dtype=torch.float32).pin_memory()
         sess = C.c_void_p()

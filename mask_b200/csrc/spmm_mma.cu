@@ -30,46 +30,16 @@
 
 #include "common.cuh"
 #include "plan.h"
+#include "spmm_common.cuh"
 
 namespace mask {
 
-struct SpmmArgs {
-    const int32_t* frag_off;
-    const int32_t* frag_win;
-    const int32_t* frag_slot;
-    const int32_t* group_off;
-    const int32_t* val_sidx;
-    const float* val_blk;      // SR-BCRS
-    const int32_t* coo_off;    // ME-TCF
-    const int32_t* coo_idx;
-    const float* coo_val;
-    const float* B;
-    int64_t ldb;
-    float* C;
-    int64_t ldc;
-    float* scratch;
-    int32_t M;
-    int32_t N;
-    int32_t relu;
-};
-
-__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%0,%1,%2,%3};\n"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ uint32_t rna_bits(float x) { return __float_as_uint(x) + 0x1000u; }
-
-__device__ __forceinline__ float4 ldg_f4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
-
-constexpr int kWarpsPerBlock = 4;
 
 // Development knobs (mask_tune): 0 = library default.
 static int g_tune_nq = 0;
 static int g_tune_min_blocks = 0;
+static int g_tune_async = 1;   // 1 = shared-memory ring fed by cp.async (SR-BCRS), 0 = register pipeline
+static int g_tune_stages = 0;
 
 template <int NQ, bool METCF, int MIN_BLOCKS>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, MIN_BLOCKS) spmm_mma_kernel(const SpmmArgs p) {
@@ -286,6 +256,16 @@ __global__ void __launch_bounds__(256) spmm_fixup_kernel(const int32_t* head_fra
     }
 }
 
+static int launch_fixup(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st) {
+    if (plan->H > 0) {
+        dim3 fgrid((unsigned)plan->H, (unsigned)((kWinRows * (a.N >> 2) + 255) / 256));
+        spmm_fixup_kernel<<<fgrid, 256, 0, st>>>(plan->d_head_frag, plan->d_frag_win, plan->d_frag_slot, plan->F,
+                                                 a.scratch, a.C, a.ldc, a.M, a.N, a.relu);
+        MASK_CUDA_TRY(cudaGetLastError());
+    }
+    return MASK_OK;
+}
+
 template <bool METCF>
 static int launch_spmm(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
     if (plan->G == 0) return MASK_OK;
@@ -296,6 +276,11 @@ static int launch_spmm(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
     // columns per warp: wide slabs (fewer re-reads of the tile values per column) when N fills
     // four warps of them, else narrower slabs so that small N still spreads over a block
     const int N = a.N;
+    if (!METCF && g_tune_async != 0) {
+        int rc = launch_spmm_async(plan, a, st, g_tune_nq, g_tune_stages);
+        if (rc != MASK_OK) return rc;
+        return launch_fixup(plan, a, st);
+    }
     int nq = N > 256 ? 4 : (N > 128 ? 2 : 1);
     if (g_tune_nq == 1 || g_tune_nq == 2 || g_tune_nq == 4) nq = g_tune_nq;
     const int cols_per_block = 32 * nq * kWarpsPerBlock;
@@ -314,13 +299,7 @@ static int launch_spmm(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
         default: spmm_mma_kernel<1, METCF, 4><<<grid, block, 0, st>>>(a); break;
     }
     MASK_CUDA_TRY(cudaGetLastError());
-    if (plan->H > 0) {
-        dim3 fgrid((unsigned)plan->H, (unsigned)((kWinRows * (N >> 2) + 255) / 256));
-        spmm_fixup_kernel<<<fgrid, 256, 0, st>>>(plan->d_head_frag, plan->d_frag_win, plan->d_frag_slot, plan->F,
-                                                 a.scratch, a.C, a.ldc, a.M, a.N, a.relu);
-        MASK_CUDA_TRY(cudaGetLastError());
-    }
-    return MASK_OK;
+    return launch_fixup(plan, a, st);
 }
 
 static int check_common(const mask_plan* plan, int32_t M, int32_t K, int32_t N, const float* B, int64_t ldb,
@@ -332,6 +311,7 @@ static int check_common(const mask_plan* plan, int32_t M, int32_t K, int32_t N, 
     if (N == 0) return MASK_OK;
     MASK_REQUIRE(B != nullptr && C != nullptr, "B or C is NULL");
     MASK_REQUIRE(ldb >= N && ldc >= N && ldb % 4 == 0 && ldc % 4 == 0, "ldb/ldc must be >= N and multiples of 4");
+    MASK_REQUIRE(ldb < ((int64_t)1 << 30), "ldb too large");
     MASK_REQUIRE((reinterpret_cast<uintptr_t>(B) & 15) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0,
                  "B and C must be 16-byte aligned");
     const size_t need = mask_plan_scratch_bytes(plan, N);
@@ -349,6 +329,8 @@ extern "C" int mask_tune(const char* name, int value) {
     MASK_REQUIRE(name != nullptr, "name is NULL");
     if (!strcmp(name, "nq")) g_tune_nq = value;
     else if (!strcmp(name, "min_blocks")) g_tune_min_blocks = value;
+    else if (!strcmp(name, "async")) g_tune_async = value;
+    else if (!strcmp(name, "stages")) g_tune_stages = value;
     else return fail(MASK_ERR_INVALID_ARGUMENT, "unknown tuning knob");
     return MASK_OK;
 }

@@ -46,8 +46,11 @@ class Plan:
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
-        if h:
-            lib().mask_plan_destroy(h)
+        if h and lib is not None:  # module globals may already be gone at interpreter exit
+            try:
+                lib().mask_plan_destroy(h)
+            except Exception:
+                pass
 
     def scratch_bytes(self, N: int) -> int:
         return int(lib().mask_plan_scratch_bytes(self._h, N))

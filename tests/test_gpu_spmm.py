@@ -80,20 +80,30 @@ def test_srbcrs_spmm_policies(oracle_mod, name, policy, gt):
     assert torch.equal(out1, out2)
 
 
-@pytest.mark.parametrize("nq,mb", [(1, 0), (2, 0), (2, 4), (4, 0), (4, 3)])
-def test_srbcrs_spmm_kernel_variants(oracle_mod, nq, mb):
+@pytest.mark.parametrize("use_async,nq,knob", [(0, 1, 0), (0, 2, 0), (0, 2, 4), (0, 4, 0), (0, 4, 3),
+                                                (1, 1, 0), (1, 1, 4), (1, 2, 0), (1, 2, 3), (1, 2, 45), (1, 2, 5),
+                                                (1, 2, 6), (1, 2, 8), (1, 4, 0), (1, 4, 3), (1, 4, 43), (1, 4, 5),
+                                                (1, 4, 6), (1, 4, 8)])
+@pytest.mark.parametrize("name,N", [("rmat12u", 512), ("hub_rows", 200), ("m33_empty_window", 64)])
+def test_srbcrs_spmm_kernel_variants(oracle_mod, name, N, use_async, nq, knob):
+    """Register-pipelined kernel (knob = occupancy target) and shared-memory ring kernel
+    (knob = ring slots per warp), every column-slab width."""
     import torch
     from mask_b200 import engine
-    m = cases.SMALL["rmat12u"]()
+    m = cases.SMALL[name]()
     rp, ci, va = _dev(m)
     p = engine.pack_srbcrs(rp, ci, va, m.M, m.K)
-    B = _dense(m.K, 512, 9)
+    B = _dense(m.K, N, 9)
     try:
+        engine.tune("async", use_async)
         engine.tune("nq", nq)
-        engine.tune("min_blocks", mb)
-        out = engine.spmm(p, torch.from_numpy(B).cuda())
+        engine.tune("stages" if use_async else "min_blocks", knob)
+        out = torch.full((m.M, N), float("nan"), device="cuda")
+        engine.spmm(p, torch.from_numpy(B).cuda(), out=out, plan=engine.Plan(p.val_soff, m.M, p.T, "auto", 3))
     finally:
+        engine.tune("async", 1)
         engine.tune("nq", 0)
+        engine.tune("stages", 0)
         engine.tune("min_blocks", 0)
     _assert_close(oracle_mod, m, B, out.cpu().numpy())
 
