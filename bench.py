@@ -138,6 +138,14 @@ def panel_bounds(m, parts: int, dev) -> list[int]:
     return balanced_panels(val_soff.cpu().numpy(), m.M, parts)
 
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the dominant kernel,
+# captured once with ncu on exactly this workload on one GPU; keyed by (workload, scale, N, format).
+NCU_TRAFFIC_BYTES = {
+    ("rmat20_gcn", None, 512, "srbcrs"): 17.31e9 + 2.33e9,   # profiles/spmm_async_kernel_rmat_n512.md
+    ("rmat20_gcn", 18, 512, "srbcrs"): 2.559e9 + 0.547e9,
+}
+
+
 def algorithmic_bytes(T: int, W: int, M: int, N: int, distinct_cols: int) -> int:
     """A values + column metadata + every touched row of B once + C written once."""
     return 4 * 128 * T + 4 * (8 * T + W + 1) + 4 * N * distinct_cols + 4 * M * N
@@ -201,12 +209,14 @@ def main():
     ap.add_argument("--format", default="srbcrs", choices=["srbcrs", "metcf"])
     ap.add_argument("--policy", default="auto")
     ap.add_argument("--group-tiles", type=int, default=0)
+    ap.add_argument("--hints", type=int, default=0, help="kernel variant: L2 eviction hints bitmask")
     ap.add_argument("--e2e-steps", type=int, default=3, help="0 skips the host-buffer leg")
     ap.add_argument("--nq", type=int, default=0, help="kernel variant: 32-column groups per warp (0 = default)")
     ap.add_argument("--min-blocks", type=int, default=0, help="kernel variant: occupancy target (0 = default)")
     ap.add_argument("--stages", type=int, default=0, help="kernel variant: ring slots per warp (0 = default)")
     ap.add_argument("--no-async", action="store_true", help="use the register-pipelined kernel")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / verification leg")
+    ap.add_argument("--no-tf32-probe", action="store_true", help="skip the dense TF32 GEMM peak measurement")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
     if args.impl == "reference":
@@ -226,6 +236,7 @@ def main():
     engine.tune("nq", args.nq)
     engine.tune("min_blocks", args.min_blocks)
     engine.tune("stages", args.stages)
+    engine.tune("hints", args.hints)
     engine.tune("async", 0 if args.no_async else 1)
 
     m, bseed = build_workload(args.workload, args.scale)
@@ -315,6 +326,28 @@ def main():
         log(f"[bench] e2e leg failed: {e}")
         host_result = None
 
+    # ---- dense TF32 GEMM peak of this GPU (denominator of the tensor-core bound) ----
+    tf32_tflops = None
+    try:
+        if args.no_tf32_probe:
+            raise RuntimeError("skipped (--no-tf32-probe)")
+        torch.backends.cuda.matmul.allow_tf32 = True
+        ga = torch.randn(8192, 8192, device=dev)
+        gb = torch.randn(8192, 8192, device=dev)
+        best = 1e9
+        for i in range(8):
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record()
+            torch.matmul(ga, gb)
+            g1.record()
+            torch.cuda.synchronize()
+            if i >= 2:
+                best = min(best, g0.elapsed_time(g1))
+        tf32_tflops = 2.0 * 8192 ** 3 / (best * 1e-3) / 1e12
+        del ga, gb
+    except Exception as e:
+        log(f"[bench] TF32 peak measurement failed: {e}")
+
     # ---- roofline of the dominant kernel (rank-local) ----
     hbm_gbs, peak_src = measured_peaks()
     W = (panel.M + 15) // 16
@@ -325,10 +358,14 @@ def main():
     kernel_ms = float(np.mean(per_launch))
     achieved = bytes_alg / (kernel_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
-                "traffic": None, "peak_source": peak_src, "bytes_algorithmic": bytes_alg,
-                "kernel_ms": kernel_ms, "kernel": "spmm_mma_kernel (+ spmm_fixup_kernel)",
+                "traffic": NCU_TRAFFIC_BYTES.get((args.workload, args.scale, N, args.format)) if world == 1 else None,
+                "peak_source": peak_src, "bytes_algorithmic": bytes_alg,
+                "kernel_ms": kernel_ms, "kernel": "spmm_async_kernel (+ spmm_fixup_kernel)",
                 "bytes_gather_no_reuse": bytes_alg - 4 * N * distinct + 4 * N * G_rows,
-                "padded_tile_tflop": 256.0 * packed.T * N / 1e12}
+                "padded_tile_tflop": 256.0 * packed.T * N / 1e12,
+                "tf32_dense_peak_tflops_measured": tf32_tflops,
+                "tensor_bound_ms": (256.0 * packed.T * N / 1e12) / tf32_tflops * 1e3 if tf32_tflops else None,
+                "hbm_bound_ms": bytes_alg / (hbm_gbs * 1e9) * 1e3}
 
     # ---- CPU baseline + verification (rank 0, single GPU only) ----
     cpu = None

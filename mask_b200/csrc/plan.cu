@@ -62,10 +62,11 @@ static void multi_bind(const int32_t* soff, int32_t W, std::vector<int32_t>& tas
 }
 
 static int32_t default_group_tiles(int64_t T) {
-    // enough groups to fill every SM several times over, large enough to amortise a block
+    // enough groups to fill every SM several times over, large enough to amortise a block's
+    // pipeline fill and to keep the number of split-window partial tiles small
     const int64_t slots = (int64_t)sm_count() * 3;
     const int64_t g = T / (slots * 4);
-    return (int32_t)std::max<int64_t>(8, std::min<int64_t>(64, g));
+    return (int32_t)std::max<int64_t>(8, std::min<int64_t>(128, g));
 }
 
 // Fills the fragment / group tables of `p` from val_soff on the host.
@@ -110,6 +111,12 @@ static void build_tables(mask_plan& p, const int32_t* soff) {
         }
         if (go.back() != (int32_t)fw.size()) go.push_back((int32_t)fw.size());
     } else {
+        // Windows are cut only when they exceed a group AND the matrix is large enough for the cut
+        // to matter: with fewer than a couple of groups per resident block, a window of up to 128
+        // tiles finishes within the single wave anyway and splitting it would only add the
+        // partial-tile round trip and the fix-up launch.
+        const int64_t per_slot = p.T / std::max<int64_t>(1, (int64_t)sm_count() * 3);
+        const int32_t split_above = std::max<int32_t>(G, (int32_t)std::min<int64_t>(2 * per_slot, 128));
         int32_t load = 0, in_group = 0;
         auto close = [&]() {
             if (go.back() != (int32_t)fw.size()) go.push_back((int32_t)fw.size());
@@ -121,9 +128,9 @@ static void build_tables(mask_plan& p, const int32_t* soff) {
                 fo.push_back(s); fw.push_back(w); close();
                 continue;
             }
-            if (x > G) {  // split into near-equal parts, one block each
+            if (x > split_above) {  // split into near-equal parts, one block each
                 close();
-                const int32_t parts = (x + G - 1) / G, base = x / parts, rem = x % parts;
+                const int32_t parts = (x + split_above - 1) / split_above, base = x / parts, rem = x % parts;
                 int32_t at = s;
                 for (int32_t i = 0; i < parts; i++) {
                     fo.push_back(at); fw.push_back(w); close();

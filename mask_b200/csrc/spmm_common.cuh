@@ -24,6 +24,7 @@ struct SpmmArgs {
     int32_t M;
     int32_t N;
     int32_t relu;
+    int32_t hints;   // bit 0: L2 eviction-priority hints on the copies, bit 1: streaming stores of C
 };
 
 __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -89,8 +90,13 @@ __device__ __forceinline__ void flush_fragment(const SpmmArgs& p, int ff, int co
             }
             if (r < rows_ok) {
                 float* row = dst + (int64_t)r * ld;
-                if (c0 < p.N) *reinterpret_cast<float4*>(row + c0) = v0;
-                if (c0 + 4 < p.N) *reinterpret_cast<float4*>(row + c0 + 4) = v1;
+                if (p.hints & 2) {  // C is written once and not read again by this kernel
+                    if (c0 < p.N) __stcs(reinterpret_cast<float4*>(row + c0), v0);
+                    if (c0 + 4 < p.N) __stcs(reinterpret_cast<float4*>(row + c0 + 4), v1);
+                } else {
+                    if (c0 < p.N) *reinterpret_cast<float4*>(row + c0) = v0;
+                    if (c0 + 4 < p.N) *reinterpret_cast<float4*>(row + c0 + 4) = v1;
+                }
             }
         }
 #pragma unroll

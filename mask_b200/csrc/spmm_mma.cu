@@ -40,6 +40,7 @@ static int g_tune_nq = 0;
 static int g_tune_min_blocks = 0;
 static int g_tune_async = 1;   // 1 = shared-memory ring fed by cp.async (SR-BCRS), 0 = register pipeline
 static int g_tune_stages = 0;
+static int g_tune_hints = 0;
 
 template <int NQ, bool METCF, int MIN_BLOCKS>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, MIN_BLOCKS) spmm_mma_kernel(const SpmmArgs p) {
@@ -276,6 +277,7 @@ static int launch_spmm(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
     // columns per warp: wide slabs (fewer re-reads of the tile values per column) when N fills
     // four warps of them, else narrower slabs so that small N still spreads over a block
     const int N = a.N;
+    a.hints = g_tune_hints;
     if (!METCF && g_tune_async != 0) {
         int rc = launch_spmm_async(plan, a, st, g_tune_nq, g_tune_stages);
         if (rc != MASK_OK) return rc;
@@ -331,6 +333,7 @@ extern "C" int mask_tune(const char* name, int value) {
     else if (!strcmp(name, "min_blocks")) g_tune_min_blocks = value;
     else if (!strcmp(name, "async")) g_tune_async = value;
     else if (!strcmp(name, "stages")) g_tune_stages = value;
+    else if (!strcmp(name, "hints")) g_tune_hints = value;
     else return fail(MASK_ERR_INVALID_ARGUMENT, "unknown tuning knob");
     return MASK_OK;
 }
