@@ -162,6 +162,31 @@ int mask_spmm_metcf(const mask_plan* plan, const int32_t* d_val_soff, const int3
                     int64_t ldb, float* d_C, int64_t ldc, void* d_scratch, size_t scratch_bytes,
                     int epilogue, void* stream);
 
+/* SR-BCRS SpMM for callers that are not allowed to allocate device memory -- a process whose
+ * whole device heap belongs to an arena of its own (an inference server, an engine that loads this
+ * library as a plug-in) or a loop that cannot afford the device-wide synchronisation of
+ * cudaMalloc/cudaFree.  It has NO COUNTERPART IN THE REFERENCE PROJECT.  Same arguments and result
+ * as mask_spmm_srbcrs minus the scratch buffer: the partial tiles of split windows go to a fixed
+ * 32 MiB array inside the library's device image (mask_static_scratch_capacity() bytes; every GPU
+ * that loads the library keeps it until the process exits).  The call itself performs no
+ * cudaMalloc / cudaFree and uses no allocating library routine.
+ *   - A plan whose partial tiles for this N exceed the capacity (mask_plan_scratch_bytes(plan, N)
+ *     > capacity; 1024 partial tiles at N = 512) is refused with MASK_ERR_SCRATCH_TOO_SMALL and
+ *     nothing is launched.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current).  Make that first call during start-up,
+ *     before any stream capture begins.
+ *   - All calls on a device share the one array and it keeps whatever the last call left in it.
+ *     Nothing in it needs clearing between calls (each call writes every partial tile before
+ *     reading it), but two calls that overlap on the GPU -- different streams, or different
+ *     threads -- race on it: serialise them, or give the others mask_spmm_srbcrs with their own
+ *     buffer. */
+size_t mask_static_scratch_capacity(void);
+int mask_spmm_srbcrs_static_scratch(const mask_plan* plan, const int32_t* d_val_soff,
+                                    const int32_t* d_val_sidx, const float* d_val_block_val,
+                                    int32_t M, int32_t K, int32_t N, const float* d_B, int64_t ldb,
+                                    float* d_C, int64_t ldc, int epilogue, void* stream);
+
 /* Development knob for kernel variants, process-wide: "nq" (32-column groups per warp: 1, 2, 4;
  * 0 = chosen from N) and "min_blocks" (occupancy target of the variant; 0 = default).  Replaces
  * the reference's tile_b environment switches SRBCRS_TILE_B / DTC_TILE_B

@@ -32,6 +32,8 @@ SIGNATURES = {
     "mask_plan_export": (C.c_int, [vp, vp, vp, vp]),
     "mask_spmm_srbcrs": (C.c_int, [vp, vp, vp, vp, i32, i32, i32, vp, i64, vp, i64, vp, sz, C.c_int, vp]),
     "mask_spmm_metcf": (C.c_int, [vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, i64, vp, i64, vp, sz, C.c_int, vp]),
+    "mask_static_scratch_capacity": (sz, []),
+    "mask_spmm_srbcrs_static_scratch": (C.c_int, [vp, vp, vp, vp, i32, i32, i32, vp, i64, vp, i64, C.c_int, vp]),
     "mask_tune": (C.c_int, [C.c_char_p, C.c_int]),
     "mask_session_create_srbcrs": (C.c_int, [i32, i32, i64, vp, vp, vp, C.c_int, C.POINTER(vp)]),
     "mask_session_create_csr": (C.c_int, [i32, i32, i64, vp, vp, vp, C.c_int, C.POINTER(vp)]),
