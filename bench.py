@@ -197,6 +197,49 @@ def run_reference(args):
     }), flush=True)
 
 
+def run_gcn(args, m, bseed, dev, rank, world):
+    """2-layer GCN forward out = A*(ReLU(A*(X*W1))*W2), features = hidden = classes = N, row-sharded
+    with the panels of Z = ReLU(A*XW1)*W2 reassembled over NCCL between the layers."""
+    import torch
+    import torch.distributed as dist
+    from mask_b200 import generators as G
+    from mask_b200.gcn import ShardedGCN2, device_ops, tile_prefix_on_device
+    N = args.n
+    X = torch.from_numpy(G.dense_normal(m.K, N, bseed)).to(dev)
+    W1 = torch.from_numpy(G.glorot_uniform(N, N, bseed + 1)).to(dev)
+    W2 = torch.from_numpy(G.glorot_uniform(N, N, bseed + 2)).to(dev)
+    pack, spmm = device_ops(dev)
+    net = ShardedGCN2(m, rank, world, pack, spmm, win_prefix=tile_prefix_on_device(m, dev), chunks=4)
+    torch.backends.cuda.matmul.allow_tf32 = True
+    for _ in range(args.warmup):
+        net.forward(X, W1, W2)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        net.forward(X, W1, W2)
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    if rank == 0:
+        flops = 2 * (2.0 * m.nnz * N) + 2 * (2.0 * m.M * N * N)
+        print(json.dumps({"metric": "2-layer GCN forward (row-sharded), ms per forward", "value": ms, "unit": "ms",
+                          "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                          "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "tf32",
+                          "data": "synthetic", "spmm_gflops_effective": 2 * 2.0 * m.nnz * N / (ms * 1e-3) / 1e9,
+                          "total_gflops_effective": flops / (ms * 1e-3) / 1e9,
+                          "config": {"workload": args.workload, "M": m.M, "nnz": m.nnz, "features": N, "chunks": 4,
+                                     "panels": net.bounds}}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -215,6 +258,7 @@ def main():
     ap.add_argument("--min-blocks", type=int, default=0, help="kernel variant: occupancy target (0 = default)")
     ap.add_argument("--stages", type=int, default=0, help="kernel variant: ring slots per warp (0 = default)")
     ap.add_argument("--no-async", action="store_true", help="use the register-pipelined kernel")
+    ap.add_argument("--gcn", action="store_true", help="time the row-sharded 2-layer GCN forward instead (extra line)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / verification leg")
     ap.add_argument("--no-tf32-probe", action="store_true", help="skip the dense TF32 GEMM peak measurement")
     args = ap.parse_args()
@@ -241,6 +285,8 @@ def main():
 
     m, bseed = build_workload(args.workload, args.scale)
     dev = torch.device("cuda", local)
+    if args.gcn:
+        return run_gcn(args, m, bseed, dev, rank, world)
     bounds = panel_bounds(m, world, dev)
     r0, r1 = bounds[rank], bounds[rank + 1]
     panel = m.row_slice(r0, r1) if world > 1 else m

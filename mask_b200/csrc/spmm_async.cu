@@ -64,7 +64,7 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
-template <int NQ, int S>
+template <int NQ, int S, int WPB = kWarpsPerBlock>
 struct AsyncLayout {
     static constexpr int kBBytes = NQ * 1024;                   // per slot: NQ groups x 8 rows x 128 B
     static constexpr int kABytes = kTileElems * 4;              // per slot: the tile of A values
@@ -72,7 +72,7 @@ struct AsyncLayout {
     static constexpr int kIdxSlots = 2 * S;
     static constexpr int kIdxBytes = kIdxSlots * kTileCols * 4;  // per warp
     static constexpr int kWarpBytes = S * kSlotBytes + kIdxBytes;
-    static constexpr int kBlockBytes = kWarpsPerBlock * kWarpBytes;
+    static constexpr int kBlockBytes = WPB * kWarpBytes;
 };
 
 // Copies of one tile's B rows, unrolled over the 32-column groups with immediate offsets.
@@ -94,17 +94,21 @@ struct CopyRows {
     }
 };
 
-// GUARD = false requires N % (32*NQ*kWarpsPerBlock) == 0 (every column group of every warp is full).
-template <int NQ, int S, int MIN_BLOCKS, bool GUARD>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32, MIN_BLOCKS) spmm_async_kernel(const SpmmArgs p) {
-    using L = AsyncLayout<NQ, S>;
+// WPB warps per block take adjacent column slabs of the same tiles.  blockIdx.y selects the
+// group of WPB slabs; blocks are dispatched x-fastest, so with WPB = 1 the whole matrix is swept
+// once per 32*NQ-column slab: the rows of B then compete for L2 with 32*NQ*4 bytes each instead of
+// 4N bytes, which is what raises the hit rate on power-law matrices.
+// GUARD = false requires N % (32*NQ*WPB) == 0 (every column group of every warp is full).
+template <int NQ, int S, int MIN_BLOCKS, bool GUARD, int WPB = kWarpsPerBlock>
+__global__ void __launch_bounds__(WPB * 32, MIN_BLOCKS) spmm_async_kernel(const SpmmArgs p) {
+    using L = AsyncLayout<NQ, S, WPB>;
     extern __shared__ __align__(128) unsigned char smem[];
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int g = lane >> 2;
     const int k = lane & 3;
-    const int col_base = (blockIdx.y * kWarpsPerBlock + warp) * (32 * NQ);
+    const int col_base = (blockIdx.y * WPB + warp) * (32 * NQ);
     if (col_base >= p.N) return;
 
     int f = p.group_off[blockIdx.x];
@@ -229,18 +233,18 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, MIN_BLOCKS) spmm_async_ke
     cp_async_wait<0>();
 }
 
-template <int NQ, int S, int MIN_BLOCKS>
+template <int NQ, int S, int MIN_BLOCKS, int WPB = kWarpsPerBlock>
 static int launch_variant(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st) {
-    using L = AsyncLayout<NQ, S>;
-    const int cols_per_block = 32 * NQ * kWarpsPerBlock;
+    using L = AsyncLayout<NQ, S, WPB>;
+    const int cols_per_block = 32 * NQ * WPB;
     const bool guard = (a.N % cols_per_block) != 0;
-    auto kern = guard ? spmm_async_kernel<NQ, S, MIN_BLOCKS, true> : spmm_async_kernel<NQ, S, MIN_BLOCKS, false>;
+    auto kern = guard ? spmm_async_kernel<NQ, S, MIN_BLOCKS, true, WPB> : spmm_async_kernel<NQ, S, MIN_BLOCKS, false, WPB>;
     // opt in to more than 48 KB of dynamic shared memory (cheap; repeated per call so that it
     // holds for whichever device is current)
     MASK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBlockBytes));
     dim3 grid((unsigned)plan->G, (unsigned)((a.N + cols_per_block - 1) / cols_per_block));
     if (grid.y > 65535) return fail(MASK_ERR_INVALID_ARGUMENT, "N too large");
-    kern<<<grid, kWarpsPerBlock * 32, L::kBlockBytes, st>>>(a);
+    kern<<<grid, WPB * 32, L::kBlockBytes, st>>>(a);
     MASK_CUDA_TRY(cudaGetLastError());
     return MASK_OK;
 }
@@ -257,6 +261,9 @@ int launch_spmm_async(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st,
                 case 5: return launch_variant<4, 5, 2>(plan, a, st);
                 case 6: return launch_variant<4, 6, 2>(plan, a, st);
                 case 8: return launch_variant<4, 8, 1>(plan, a, st);
+                case 104: return launch_variant<4, 4, 12, 1>(plan, a, st);   // one warp per block: 128-column slabs
+                case 106: return launch_variant<4, 6, 8, 1>(plan, a, st);
+                case 204: return launch_variant<4, 4, 6, 2>(plan, a, st);    // two warps per block: 256-column slabs
                 default: return launch_variant<4, 4, 2>(plan, a, st);
             }
         case 2:
@@ -266,6 +273,8 @@ int launch_spmm_async(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st,
                 case 5: return launch_variant<2, 5, 4>(plan, a, st);
                 case 6: return launch_variant<2, 6, 3>(plan, a, st);
                 case 8: return launch_variant<2, 8, 2>(plan, a, st);
+                case 104: return launch_variant<2, 4, 16, 1>(plan, a, st);   // one warp per block: 64-column slabs
+                case 108: return launch_variant<2, 8, 12, 1>(plan, a, st);
                 default: return launch_variant<2, 4, 4>(plan, a, st);
             }
         default:

@@ -1,0 +1,157 @@
+"""Host-side logic of the multi-GPU path on CPU: panel/chunk partitioning, and the row-sharded
+2-layer GCN forward run by two gloo ranks (the per-panel SpMM is the oracle's CPU product here;
+on a GPU the same harness gets the device kernels)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from mask_b200 import generators as G
+from mask_b200.gcn import ShardedGCN2, chunk_bounds
+from mask_b200.sharding import balanced_panels, nnz_balanced_panels
+
+
+def test_panels_are_window_aligned_and_balanced():
+    m = G.rmat_gcn_normalised(scale=12, samples_per_node=8, seed=201)
+    for parts in (1, 2, 3, 4, 8):
+        b = nnz_balanced_panels(m.rowptr, m.M, parts)
+        assert b[0] == 0 and b[-1] == m.M and len(b) == parts + 1
+        assert all(x % 16 == 0 for x in b[:-1]) and all(x <= y for x, y in zip(b, b[1:]))
+        share = [int(m.rowptr[y] - m.rowptr[x]) for x, y in zip(b, b[1:])]
+        assert max(share) - min(share) <= 2 * int(np.diff(m.rowptr).max()) * 16 + 1
+    # ragged M, generic cost prefix, more parts than windows
+    prefix = np.array([0, 5, 5, 9], dtype=np.int64)
+    assert balanced_panels(prefix, 40, 2) in ([0, 16, 40], [0, 32, 40])
+    b = balanced_panels(prefix, 40, 8)
+    assert b[0] == 0 and b[-1] == 40 and all(x <= y for x, y in zip(b, b[1:]))
+    assert chunk_bounds(prefix, 40, 16, 40, 2)[0] == 16 and chunk_bounds(prefix, 40, 16, 40, 2)[-1] == 40
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _cpu_ops():
+    import oracle
+
+    def pack(csr):
+        return csr
+
+    def spmm(csr, dense, relu):
+        out = torch.from_numpy(oracle.spmm_f32(csr.M, csr.rowptr, csr.colind, csr.values, dense.numpy(), threads=1))
+        return torch.relu(out) if relu else out
+
+    return pack, spmm
+
+
+def _rank_main(rank, world, port, chunks, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        m = G.rmat_gcn_normalised(scale=9, samples_per_node=6, seed=501)
+        X = torch.from_numpy(G.dense_normal(m.K, 24, 502))
+        W1 = torch.from_numpy(G.glorot_uniform(24, 16, 503))
+        W2 = torch.from_numpy(G.glorot_uniform(16, 8, 504))
+        pack, spmm = _cpu_ops()
+        net = ShardedGCN2(m, rank, world, pack, spmm, chunks=chunks)
+        out = net.forward(X, W1, W2)
+        q.put((rank, net.bounds, out.numpy()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,chunks", [(2, 3), (3, 1)])
+def test_sharded_gcn_forward_matches_single_process(world, chunks):
+    import oracle
+    m = G.rmat_gcn_normalised(scale=9, samples_per_node=6, seed=501)
+    X = G.dense_normal(m.K, 24, 502)
+    W1, W2 = G.glorot_uniform(24, 16, 503), G.glorot_uniform(16, 8, 504)
+    h1 = np.maximum(oracle.spmm_f32(m.M, m.rowptr, m.colind, m.values, X @ W1, threads=1), 0)
+    want = oracle.spmm_f32(m.M, m.rowptr, m.colind, m.values, h1 @ W2, threads=1)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, chunks, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    full = np.zeros_like(want)
+    for rank, bounds, out in got:
+        full[bounds[rank]:bounds[rank + 1]] = out
+    assert np.allclose(full, want, rtol=1e-5, atol=1e-6)
+
+
+def _gpu_rank_main(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from mask_b200.gcn import device_ops, tile_prefix_on_device
+        dev = torch.device("cuda", rank)
+        m = G.rmat_gcn_normalised(scale=12, samples_per_node=8, seed=501)
+        X = torch.from_numpy(G.dense_normal(m.K, 64, 502)).to(dev)
+        W1 = torch.from_numpy(G.glorot_uniform(64, 64, 503)).to(dev)
+        W2 = torch.from_numpy(G.glorot_uniform(64, 32, 504)).to(dev)
+        pack, spmm = device_ops(dev)
+        net = ShardedGCN2(m, rank, world, pack, spmm, win_prefix=tile_prefix_on_device(m, dev), chunks=3)
+        out = net.forward(X, W1, W2)
+        torch.cuda.synchronize()
+        q.put((rank, net.bounds, out.cpu().numpy()))
+    finally:
+        dist.destroy_process_group()
+
+
+def _gcn_reference(m, X, W1, W2):
+    import oracle
+    h1 = np.maximum(oracle.spmm_f32(m.M, m.rowptr, m.colind, m.values, X @ W1), 0)
+    return oracle.spmm_f32(m.M, m.rowptr, m.colind, m.values, h1 @ W2)
+
+
+@pytest.mark.gpu
+def test_gcn_forward_single_gpu():
+    from mask_b200.gcn import device_ops, tile_prefix_on_device
+    dev = torch.device("cuda", 0)
+    m = G.rmat_gcn_normalised(scale=12, samples_per_node=8, seed=501)
+    X, W1, W2 = G.dense_normal(m.K, 64, 502), G.glorot_uniform(64, 64, 503), G.glorot_uniform(64, 32, 504)
+    pack, spmm = device_ops(dev)
+    net = ShardedGCN2(m, 0, 1, pack, spmm, win_prefix=tile_prefix_on_device(m, dev), chunks=3)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    out = net.forward(*(torch.from_numpy(a).to(dev) for a in (X, W1, W2))).cpu().numpy()
+    want = _gcn_reference(m, X, W1, W2)
+    # two chained TF32 products: compare at the scale of the result
+    assert np.abs(out - want).max() <= 4e-3 * np.abs(want).max() + 1e-6
+
+
+@pytest.mark.gpu
+def test_gcn_forward_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    m = G.rmat_gcn_normalised(scale=12, samples_per_node=8, seed=501)
+    X, W1, W2 = G.dense_normal(m.K, 64, 502), G.glorot_uniform(64, 64, 503), G.glorot_uniform(64, 32, 504)
+    want = _gcn_reference(m, X, W1, W2)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gpu_rank_main, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=300) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    full = np.zeros_like(want)
+    for rank, bounds, out in got:
+        full[bounds[rank]:bounds[rank + 1]] = out
+    assert np.abs(full - want).max() <= 4e-3 * np.abs(want).max() + 1e-6
