@@ -134,6 +134,10 @@ size_t mask_plan_scratch_bytes(const mask_plan* plan, int32_t N);
 /* Introspection for tests: numbers of fragments, groups, split fragments, and the group size. */
 int mask_plan_info(const mask_plan* plan, int64_t* n_frag, int64_t* n_groups, int64_t* n_partial,
                    int32_t* group_tiles);
+/* Reads the plan's device status word (synchronises): 0, or non-zero if a kernel launched with
+ * this plan gave up on one of its bounded waits (its output is then invalid).  No counterpart in
+ * the reference, whose kernels have no waits. */
+int mask_plan_status(const mask_plan* plan, int32_t* h_status, void* stream);
 /* Copies the plan tables to host arrays (frag_offset[F+1], frag_window[F], group_offset[G+1]). */
 int mask_plan_export(const mask_plan* plan, int32_t* frag_offset, int32_t* frag_window,
                      int32_t* group_offset);

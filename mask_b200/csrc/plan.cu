@@ -160,6 +160,9 @@ static void build_tables(mask_plan& p, const int32_t* soff) {
         }
     }
     p.H = (int64_t)p.h_head_frag.size();
+    p.max_group_tiles = 0;
+    for (int64_t g = 0; g < p.G; g++)
+        p.max_group_tiles = std::max<int32_t>(p.max_group_tiles, fo[go[g + 1]] - fo[go[g]]);
 }
 
 template <typename T>
@@ -233,6 +236,7 @@ extern "C" int mask_plan_create(const int32_t* d_val_soff, int32_t M, int64_t T,
     if (rc == MASK_OK) rc = upload(p->h_frag_slot, &p->d_frag_slot, st);
     if (rc == MASK_OK) rc = upload(p->h_group_off, &p->d_group_off, st);
     if (rc == MASK_OK) rc = upload(p->h_head_frag, &p->d_head_frag, st);
+    if (rc == MASK_OK) rc = upload(std::vector<int32_t>(4, 0), &p->d_status, st);
     if (rc == MASK_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = fail(MASK_ERR_CUDA, "plan upload failed");
     if (rc != MASK_OK) {
         mask_plan_destroy(p);
@@ -249,6 +253,7 @@ extern "C" void mask_plan_destroy(mask_plan* p) {
     cudaFree(p->d_frag_slot);
     cudaFree(p->d_group_off);
     cudaFree(p->d_head_frag);
+    cudaFree(p->d_status);
     delete p;
 }
 
@@ -265,6 +270,15 @@ extern "C" int mask_plan_info(const mask_plan* p, int64_t* n_frag, int64_t* n_gr
     if (n_groups) *n_groups = p->G;
     if (n_partial) *n_partial = p->P;
     if (group_tiles) *group_tiles = p->group_tiles;
+    return MASK_OK;
+}
+
+extern "C" int mask_plan_status(const mask_plan* p, int32_t* h_status, void* stream) {
+    using namespace mask;
+    MASK_REQUIRE(p != nullptr && h_status != nullptr, "NULL argument");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    MASK_CUDA_TRY(cudaMemcpyAsync(h_status, p->d_status, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+    MASK_CUDA_TRY(cudaStreamSynchronize(st));
     return MASK_OK;
 }
 

@@ -22,10 +22,12 @@ struct mask_plan {
     int64_t G = 0;  // groups (thread blocks)
     int64_t P = 0;  // fragments that are part of a split window
     int64_t H = 0;  // split windows
+    int32_t max_group_tiles = 0;  // most tiles any thread block gets
     std::vector<int32_t> h_frag_off, h_frag_win, h_frag_slot, h_group_off, h_head_frag;
     int32_t* d_frag_off = nullptr;
     int32_t* d_frag_win = nullptr;
     int32_t* d_frag_slot = nullptr;
     int32_t* d_group_off = nullptr;
     int32_t* d_head_frag = nullptr;
+    int32_t* d_status = nullptr;  // device status word: non-zero after a kernel gave up on a bounded wait
 };

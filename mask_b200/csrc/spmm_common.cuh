@@ -106,6 +106,11 @@ __device__ __forceinline__ void flush_fragment(const SpmmArgs& p, int ff, int co
     }
 }
 
+// spmm_umma.cu: tcgen05 / tensor-memory variant (SR-BCRS, N % 512 == 0, groups of at most
+// kUmmaMaxGroupTiles tiles).
+constexpr int kUmmaMaxGroupTiles = 256;
+int launch_spmm_umma(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st);
+
 // spmm_async.cu: shared-memory ring variant (SR-BCRS).  nq / stages 0 = defaults.
 int launch_spmm_async(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int nq, int stages);
 

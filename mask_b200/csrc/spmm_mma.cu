@@ -41,6 +41,7 @@ static int g_tune_min_blocks = 0;
 static int g_tune_async = 1;   // 1 = shared-memory ring fed by cp.async (SR-BCRS), 0 = register pipeline
 static int g_tune_stages = 0;
 static int g_tune_hints = 0;
+static int g_tune_umma = 0;    // 1 = tcgen05 kernel where it applies
 
 template <int NQ, bool METCF, int MIN_BLOCKS>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, MIN_BLOCKS) spmm_mma_kernel(const SpmmArgs p) {
@@ -278,6 +279,11 @@ static int launch_spmm(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
     // four warps of them, else narrower slabs so that small N still spreads over a block
     const int N = a.N;
     a.hints = g_tune_hints;
+    if (!METCF && g_tune_umma != 0 && N % 512 == 0 && plan->max_group_tiles <= kUmmaMaxGroupTiles) {
+        int rc = launch_spmm_umma(plan, a, st);
+        if (rc != MASK_OK) return rc;
+        return launch_fixup(plan, a, st);
+    }
     if (!METCF && g_tune_async != 0) {
         int rc = launch_spmm_async(plan, a, st, g_tune_nq, g_tune_stages);
         if (rc != MASK_OK) return rc;
@@ -334,6 +340,7 @@ extern "C" int mask_tune(const char* name, int value) {
     else if (!strcmp(name, "async")) g_tune_async = value;
     else if (!strcmp(name, "stages")) g_tune_stages = value;
     else if (!strcmp(name, "hints")) g_tune_hints = value;
+    else if (!strcmp(name, "umma")) g_tune_umma = value;
     else return fail(MASK_ERR_INVALID_ARGUMENT, "unknown tuning knob");
     return MASK_OK;
 }

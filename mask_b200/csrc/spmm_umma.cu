@@ -1,0 +1,307 @@
+// SR-BCRS 16x8 SpMM on the 5th-generation tensor cores: tcgen05.mma (TF32) with accumulators in
+// tensor memory, operands staged in shared memory by warp-specialised producers.
+//
+// Mapping.  A 16-row window is far too short for the MMA's M (64/128), so the product is issued
+// TRANSPOSED: for every tile t of window w and every 128-column slab of B,
+//
+//     D^T[128 columns x 16 rows] += Bg^T[128 x 8] * Atile^T[8 x 16]
+//
+// MMA-M = 128 output columns, MMA-N = 16 window rows, MMA-K = 8 condensed columns: no padding
+// beyond the format's own 16x8 tile.  Operands:
+//   * MMA "A" = the 8 gathered rows of B, which are contiguous along the MMA-M direction: an
+//     MN-major operand.  For 32-bit element types the only MN-major shared-memory layout the
+//     tensor core accepts is the 128-byte swizzle with a 32-byte base: atoms of 32 columns x 4
+//     rows (4 x 128 bytes), the 32-byte chunk q of row r stored at chunk q ^ (r % 4); the two
+//     4-row halves of a tile 512 bytes apart (stride byte offset), 32-column atoms 1024 bytes
+//     apart (leading byte offset).  A descriptor with the plain 128-byte swizzle is accepted but
+//     multiplies zeros (found with a one-instruction known-answer test).  Producer warps fill the
+//     layout with cp.async using lane -> (row, 16-byte chunk), so every quarter-warp reads one
+//     contiguous 128-byte line of B and writes one full, bank-conflict-free row.
+//   * MMA "B" = the stored tile itself.  SR-BCRS stores element (r,c) at Swizzle<2,2,3>(8r+c) of
+//     a row-major 16x8 float tile; in bytes that is the canonical K-major SWIZZLE_32B layout
+//     (row pitch 32 B, 8-row groups 256 B apart) except that rows 8..15 are swapped pairwise.
+//     So the 512-byte tile is copied verbatim and used as the operand; MMA-N index n then stands
+//     for window row n ^ (n >> 3), which the epilogue undoes when it stores.
+// Operand precision: the tensor core truncates FP32 to TF32.  The tile values are rounded to
+// nearest (ties away) in place before use, like the reference kernel's cvt.rna; the gathered B
+// values cannot be touched on their way from global to shared memory and are truncated.  Worst
+// case per product 2^-10 + 2^-11 = 1.46e-3 relative, inside the 2e-3 contract.
+//
+// Roles (288 threads): warps 0-3 epilogue (tensor-memory lanes 32w..32w+31 = columns of a slab),
+// warp 4 issues the MMAs (one elected lane) and rounds the tile, warps 5-8 produce.  Rings:
+// full[s] (producers -> MMA, completed by cp.async.mbarrier.arrive of 128 threads), empty[s]
+// (tcgen05.commit -> producers), acc_full/acc_empty[2] (double-buffered accumulators, 64 tensor
+// memory columns each, so the epilogue of one window overlaps the MMAs of the next).
+//
+// Every wait is bounded (about a second of SM clock): on expiry the block raises a shared abort
+// flag and a device status word, drains its copies, frees its tensor memory and returns.
+#include "spmm_common.cuh"
+
+namespace mask {
+
+constexpr int kUmmaThreads = 288;
+constexpr int kUmmaStages = 6;
+constexpr int kUmmaSlabs = 4;                       // 4 x 128 = 512 columns per block
+constexpr int kUmmaBBytes = kUmmaSlabs * 4096;      // gathered rows of one tile
+constexpr int kUmmaABytes = 512;
+constexpr int kUmmaIdsBytes = kUmmaMaxGroupTiles * kTileCols * 4;
+constexpr int kUmmaTmemCols = 128;
+constexpr long long kUmmaWaitCycles = 2000000000LL;
+
+struct UmmaLayout {
+    static constexpr int kB = 0;
+    static constexpr int kA = kUmmaStages * kUmmaBBytes;
+    static constexpr int kIds = kA + kUmmaStages * kUmmaABytes;
+    static constexpr int kBars = kIds + kUmmaIdsBytes;            // full[S], empty[S], acc_full[2], acc_empty[2]
+    static constexpr int kTmemSlot = kBars + (2 * kUmmaStages + 4) * 8;
+    static constexpr int kAbort = kTmemSlot + 8;
+    static constexpr int kBytes = kAbort + 8;
+    static constexpr int kDynamicBytes = kBytes + 1024;           // room to align the base to 1024 B
+};
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false if the block is aborting (this wait or somebody else's ran out of time).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_test(bar, parity)) return true;
+    const long long start = clock64();
+    while (true) {
+        if (mbar_test(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - start > kUmmaWaitCycles) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo16, uint32_t sbo16, uint32_t layout) {
+    // bits [0,14) start address >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4,
+    // [46,48) descriptor version (1 on sm_100), [61,64) swizzle mode
+    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)(lbo16 & 0x3FFF) << 16) | ((uint64_t)(sbo16 & 0x3FFF) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)layout << 61);
+}
+constexpr uint32_t kSwizzle128B32B = 1, kSwizzle32B = 6;   // 128-byte swizzle with 32-byte base; 32-byte swizzle
+// instruction descriptor: D = F32, A = B = TF32, A MN-major, B K-major, N = 16, M = 128
+constexpr uint32_t kUmmaIdesc = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | (0u << 16) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(kUmmaIdesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void cp16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+__global__ void __launch_bounds__(kUmmaThreads, 2) spmm_umma_kernel(const SpmmArgs p, int32_t* status) {
+    extern __shared__ unsigned char umma_smem_raw[];
+    const uint32_t raw = (uint32_t)__cvta_generic_to_shared(umma_smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;            // swizzle patterns are functions of the address bits
+    unsigned char* gbase = umma_smem_raw + (base - raw);
+    using L = UmmaLayout;
+    const uint32_t bars = base + L::kBars;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (kUmmaStages + s); };
+    auto accf_bar = [&](int b) { return bars + 8u * (2 * kUmmaStages + b); };
+    auto acce_bar = [&](int b) { return bars + 8u * (2 * kUmmaStages + 2 + b); };
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + L::kAbort);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + L::kTmemSlot);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int f0 = p.group_off[blockIdx.x], f_end = p.group_off[blockIdx.x + 1];
+    const int t0 = p.frag_off[f0];
+    const int n_tiles = p.frag_off[f_end] - t0;   // <= kUmmaMaxGroupTiles (checked by the launcher)
+    const int col0 = blockIdx.y * (kUmmaSlabs * 128);
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < kUmmaStages; s++) {
+            mbar_init(full_bar(s), 128);   // one deferred arrive per producer thread
+            mbar_init(empty_bar(s), 1);    // tcgen05.commit
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(accf_bar(b), 1);     // tcgen05.commit
+            mbar_init(acce_bar(b), 4);     // lane 0 of every epilogue warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(base + L::kTmemSlot),
+                     "r"(kUmmaTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (warp >= 5) {  // gathered-row ids of the whole group, once
+        const int pt = tid - 160;
+        const int chunks = n_tiles * 2;
+        for (int c = pt; c < chunks; c += 128) cp16(base + L::kIds + c * 16, p.val_sidx + (int64_t)t0 * kTileCols + c * 4);
+        asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp >= 5) {
+        // ------------------------------ producers ------------------------------------------------
+        const int pw = warp - 5;                 // slab of this warp
+        const int lr = lane >> 3, lc = lane & 7; // row (and row + 4), 16-byte chunk
+        const uint32_t off0 = (uint32_t)(lr * 128 + ((lc ^ (2 * lr)) * 16));   // 32-byte chunks swizzled by row % 4
+        const uint32_t off1 = off0 + 512;                                     // row + 4: same swizzle phase
+        const char* Bcol = reinterpret_cast<const char*>(p.B + col0 + 128 * pw + 4 * lc);
+        const uint32_t ldb_bytes = (uint32_t)(p.ldb * 4);
+        const int* ids = reinterpret_cast<const int*>(gbase + L::kIds);
+        int s = 0;
+        uint32_t round = 0;
+        for (int rel = 0; rel < n_tiles; rel++) {
+            if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag)) break;
+            const char* r0 = Bcol + (uint64_t)(uint32_t)ids[rel * kTileCols + lr] * ldb_bytes;
+            const char* r1 = Bcol + (uint64_t)(uint32_t)ids[rel * kTileCols + lr + 4] * ldb_bytes;
+            const uint32_t dst = base + L::kB + s * kUmmaBBytes + pw * 4096;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                cp16(dst + j * 1024 + off0, r0 + j * 128);
+                cp16(dst + j * 1024 + off1, r1 + j * 128);
+            }
+            if (pw == 0) cp16(base + L::kA + s * kUmmaABytes + lane * 16, p.val_blk + (int64_t)(t0 + rel) * kTileElems + lane * 4);
+            // arrives on full[s] once every copy this thread has issued so far has landed
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(full_bar(s)) : "memory");
+            if (++s == kUmmaStages) { s = 0; round++; }
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+    } else if (warp == 4) {
+        // ------------------------------ MMA issuer -----------------------------------------------
+        int s = 0;
+        uint32_t round = 0, uses[2] = {0, 0};
+        int buf = 0;
+        bool ok = true;
+        for (int f = f0; f < f_end && ok; f++) {
+            const int n = p.frag_off[f + 1] - p.frag_off[f];
+            if (n == 0) continue;
+            if (uses[buf] > 0 && !mbar_wait(acce_bar(buf), (uses[buf] - 1) & 1, abort_flag)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            for (int i = 0; i < n; i++) {
+                if (!mbar_wait(full_bar(s), round & 1, abort_flag)) { ok = false; break; }
+                // round the tile values to TF32 (nearest, ties away) in place
+                uint4* at = reinterpret_cast<uint4*>(gbase + L::kA + s * kUmmaABytes) + lane;
+                uint4 v = *at;
+                v.x += 0x1000u; v.y += 0x1000u; v.z += 0x1000u; v.w += 0x1000u;
+                *at = v;
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    const uint64_t bdesc = umma_smem_desc(base + L::kA + s * kUmmaABytes, 1, 16, kSwizzle32B);
+#pragma unroll
+                    for (int slab = 0; slab < kUmmaSlabs; slab++) {
+                        const uint64_t adesc = umma_smem_desc(base + L::kB + s * kUmmaBBytes + slab * 4096, 64, 32, kSwizzle128B32B);
+                        umma_tf32(tmem_base + buf * 64 + slab * 16, adesc, bdesc, i > 0 ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(s));   // the slot is free once these MMAs have read it
+                }
+                __syncwarp();
+                if (++s == kUmmaStages) { s = 0; round++; }
+            }
+            if (!ok) break;
+            if (lane == 0) umma_commit(accf_bar(buf));  // accumulators of this fragment complete
+            __syncwarp();
+            uses[buf]++;
+            buf ^= 1;
+        }
+    } else {
+        // ------------------------------ epilogue -------------------------------------------------
+        uint32_t uses[2] = {0, 0};
+        int buf = 0;
+        const int col = col0 + 32 * warp + lane;   // + 128 * slab
+        for (int f = f0; f < f_end; f++) {
+            const int n = p.frag_off[f + 1] - p.frag_off[f];
+            const int w = p.frag_win[f];
+            const int slot = p.frag_slot[f];
+            float* dst;
+            int64_t ld;
+            int rows_ok;
+            if (slot < 0) { dst = p.C + (int64_t)w * kWinRows * p.ldc; ld = p.ldc; rows_ok = p.M - w * kWinRows; }
+            else { dst = p.scratch + (int64_t)slot * kWinRows * p.N; ld = p.N; rows_ok = kWinRows; }
+            const bool relu = p.relu && slot < 0;
+            uint32_t v[kUmmaSlabs][16];
+            if (n == 0) {
+#pragma unroll
+                for (int sl = 0; sl < kUmmaSlabs; sl++)
+#pragma unroll
+                    for (int i = 0; i < 16; i++) v[sl][i] = 0u;
+            } else {
+                if (!mbar_wait(accf_bar(buf), uses[buf] & 1, abort_flag)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t taddr = tmem_base + ((uint32_t)(32 * warp) << 16) + buf * 64;
+#pragma unroll
+                for (int sl = 0; sl < kUmmaSlabs; sl++) tmem_ld16(taddr + sl * 16, v[sl]);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acce_bar(buf));   // the MMA warp may reuse this buffer
+                uses[buf]++;
+                buf ^= 1;
+            }
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const int r = i ^ (i >> 3);   // MMA-N index -> window row (rows 8..15 swapped pairwise)
+                if (r < rows_ok) {
+#pragma unroll
+                    for (int sl = 0; sl < kUmmaSlabs; sl++) {
+                        float x = __uint_as_float(v[sl][i]);
+                        if (relu) x = fmaxf(x, 0.f);
+                        dst[(int64_t)r * ld + col + 128 * sl] = x;
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- teardown: everybody gets here, aborting or not ---------------------------------------------
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 4) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kUmmaTmemCols) : "memory");
+    }
+    if (tid == 0 && *abort_flag) atomicExch(status, 1);
+}
+
+int launch_spmm_umma(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st) {
+    if (a.N % (kUmmaSlabs * 128) != 0) return fail(MASK_ERR_INVALID_ARGUMENT, "the tcgen05 kernel needs N % 512 == 0");
+    if (plan->max_group_tiles > kUmmaMaxGroupTiles) return fail(MASK_ERR_INVALID_ARGUMENT, "plan groups too large for the tcgen05 kernel");
+    MASK_CUDA_TRY(cudaFuncSetAttribute(spmm_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, UmmaLayout::kDynamicBytes));
+    dim3 grid((unsigned)plan->G, (unsigned)(a.N / (kUmmaSlabs * 128)));
+    if (grid.y > 65535) return fail(MASK_ERR_INVALID_ARGUMENT, "N too large");
+    spmm_umma_kernel<<<grid, kUmmaThreads, UmmaLayout::kDynamicBytes, st>>>(a, plan->d_status);
+    MASK_CUDA_TRY(cudaGetLastError());
+    return MASK_OK;
+}
+
+}  // namespace mask

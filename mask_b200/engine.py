@@ -60,6 +60,12 @@ class Plan:
         check(lib().mask_plan_info(self._h, C.byref(f), C.byref(g), C.byref(p), C.byref(gt)), "mask_plan_info")
         return dict(fragments=f.value, groups=g.value, partial=p.value, group_tiles=gt.value)
 
+    def status(self) -> int:
+        """Device status word: non-zero if a kernel using this plan gave up on a bounded wait."""
+        v = C.c_int32(0)
+        check(lib().mask_plan_status(self._h, C.byref(v), _stream()), "mask_plan_status")
+        return int(v.value)
+
     def export(self):
         """Host copies of (frag_offset[F+1], frag_window[F], group_offset[G+1])."""
         i = self.info()

@@ -215,3 +215,31 @@ def test_medium_rmat_against_oracle(oracle_mod):
     pm = engine.pack_metcf(rp, ci, va, m.M, m.K)
     out2 = engine.spmm(pm, torch.from_numpy(B).cuda())
     _assert_close(oracle_mod, m, B, out2.cpu().numpy())
+
+
+@pytest.mark.parametrize("name,N,gt", [("m1", 512, 0), ("m17", 512, 0), ("m33_empty_window", 512, 0), ("all_empty", 512, 0),
+                                       ("hub_rows", 512, 3), ("hub_rows", 1024, 0), ("rmat12u", 512, 0),
+                                       ("rmat12u", 512, 200), ("stencil8", 1024, 0), ("three_four_tiles", 512, 1)])
+def test_srbcrs_spmm_tcgen05_kernel(oracle_mod, name, N, gt):
+    """The tcgen05 / tensor-memory kernel (N a multiple of 512): same contract, its bounded waits
+    must not have expired, and results are deterministic.  Operand B is truncated to TF32 by the
+    tensor core (the tile values are rounded), which stays inside the product tolerance."""
+    import torch
+    from mask_b200 import engine
+    m = cases.SMALL[name]()
+    rp, ci, va = _dev(m)
+    p = engine.pack_srbcrs(rp, ci, va, m.M, m.K)
+    B = _dense(m.K, N, 41)
+    Bd = torch.from_numpy(B).cuda()
+    plan = engine.Plan(p.val_soff, m.M, p.T, "auto", gt)
+    try:
+        engine.tune("umma", 1)
+        out = torch.full((m.M, N), float("nan"), device="cuda")
+        engine.spmm(p, Bd, out=out, plan=plan)
+        out2 = torch.full((m.M, N), float("nan"), device="cuda")
+        engine.spmm(p, Bd, out=out2, plan=plan, relu=True)
+    finally:
+        engine.tune("umma", 0)
+    assert plan.status() == 0
+    _assert_close(oracle_mod, m, B, out.cpu().numpy())
+    assert torch.equal(torch.relu(out), out2)
