@@ -253,6 +253,7 @@ def main():
     ap.add_argument("--policy", default="auto")
     ap.add_argument("--group-tiles", type=int, default=0)
     ap.add_argument("--hints", type=int, default=0, help="kernel variant: L2 eviction hints bitmask")
+    ap.add_argument("--umma", type=int, default=0, help="1 = tcgen05 / tensor-memory kernel")
     ap.add_argument("--e2e-steps", type=int, default=3, help="0 skips the host-buffer leg")
     ap.add_argument("--nq", type=int, default=0, help="kernel variant: 32-column groups per warp (0 = default)")
     ap.add_argument("--min-blocks", type=int, default=0, help="kernel variant: occupancy target (0 = default)")
@@ -281,6 +282,7 @@ def main():
     engine.tune("min_blocks", args.min_blocks)
     engine.tune("stages", args.stages)
     engine.tune("hints", args.hints)
+    engine.tune("umma", args.umma)
     engine.tune("async", 0 if args.no_async else 1)
 
     m, bseed = build_workload(args.workload, args.scale)

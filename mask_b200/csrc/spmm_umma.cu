@@ -27,11 +27,16 @@
 // values cannot be touched on their way from global to shared memory and are truncated.  Worst
 // case per product 2^-10 + 2^-11 = 1.46e-3 relative, inside the 2e-3 contract.
 //
-// Roles (288 threads): warps 0-3 epilogue (tensor-memory lanes 32w..32w+31 = columns of a slab),
-// warp 4 issues the MMAs (one elected lane) and rounds the tile, warps 5-8 produce.  Rings:
-// full[s] (producers -> MMA, completed by cp.async.mbarrier.arrive of 128 threads), empty[s]
-// (tcgen05.commit -> producers), acc_full/acc_empty[2] (double-buffered accumulators, 64 tensor
-// memory columns each, so the epilogue of one window overlaps the MMAs of the next).
+// Roles (352 threads): warps 0-3 epilogue (tensor-memory lanes 32w..32w+31 = columns of a slab),
+// warp 4 issues the MMAs (one elected lane), warps 5-6 prepare (round the tile values of
+// alternate tiles and make the copied data visible to the tensor core's asynchronous proxy),
+// warps 7-10 produce.  cp.async writes through the generic proxy, so a fence.proxy.async has to
+// sit between a stage's arrival and its MMAs; doing that (and the rounding) inside the issuing
+// warp serialised ~15 % of the kernel's time into one warp, hence the separate, two-way
+// interleaved preparation stage.  Rings: full[s] (producers -> prepare, completed by
+// cp.async.mbarrier.arrive of 128 threads), ready[s] (prepare -> MMA), empty[s] (tcgen05.commit ->
+// producers), acc_full/acc_empty[2] (double-buffered accumulators, 64 tensor-memory columns each,
+// so the epilogue of one window overlaps the MMAs of the next).
 //
 // Every wait is bounded (about a second of SM clock): on expiry the block raises a shared abort
 // flag and a device status word, drains its copies, frees its tensor memory and returns.
@@ -39,7 +44,7 @@
 
 namespace mask {
 
-constexpr int kUmmaThreads = 288;
+constexpr int kUmmaThreads = 352;
 constexpr int kUmmaStages = 6;
 constexpr int kUmmaSlabs = 4;                       // 4 x 128 = 512 columns per block
 constexpr int kUmmaBBytes = kUmmaSlabs * 4096;      // gathered rows of one tile
@@ -52,8 +57,8 @@ struct UmmaLayout {
     static constexpr int kB = 0;
     static constexpr int kA = kUmmaStages * kUmmaBBytes;
     static constexpr int kIds = kA + kUmmaStages * kUmmaABytes;
-    static constexpr int kBars = kIds + kUmmaIdsBytes;            // full[S], empty[S], acc_full[2], acc_empty[2]
-    static constexpr int kTmemSlot = kBars + (2 * kUmmaStages + 4) * 8;
+    static constexpr int kBars = kIds + kUmmaIdsBytes;            // full[S], empty[S], ready[S], acc_full[2], acc_empty[2]
+    static constexpr int kTmemSlot = kBars + (3 * kUmmaStages + 4) * 8;
     static constexpr int kAbort = kTmemSlot + 8;
     static constexpr int kBytes = kAbort + 8;
     static constexpr int kDynamicBytes = kBytes + 1024;           // room to align the base to 1024 B
@@ -65,10 +70,13 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// try_wait parks the thread in hardware until the phase completes or a short, implementation-defined
+// time slice ends, so a waiting warp costs almost no issue slots (a test_wait spin loop here made the
+// idle epilogue warps execute as many instructions as the whole kernel needs).
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(bar), "r"(parity)
         : "memory");
@@ -129,8 +137,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) spmm_umma_kernel(const SpmmAr
     const uint32_t bars = base + L::kBars;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (kUmmaStages + s); };
-    auto accf_bar = [&](int b) { return bars + 8u * (2 * kUmmaStages + b); };
-    auto acce_bar = [&](int b) { return bars + 8u * (2 * kUmmaStages + 2 + b); };
+    auto ready_bar = [&](int s) { return bars + 8u * (2 * kUmmaStages + s); };
+    auto accf_bar = [&](int b) { return bars + 8u * (3 * kUmmaStages + b); };
+    auto acce_bar = [&](int b) { return bars + 8u * (3 * kUmmaStages + 2 + b); };
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + L::kAbort);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + L::kTmemSlot);
 
@@ -145,6 +154,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) spmm_umma_kernel(const SpmmAr
         for (int s = 0; s < kUmmaStages; s++) {
             mbar_init(full_bar(s), 128);   // one deferred arrive per producer thread
             mbar_init(empty_bar(s), 1);    // tcgen05.commit
+            mbar_init(ready_bar(s), 1);    // lane 0 of the preparing warp
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(accf_bar(b), 1);     // tcgen05.commit
@@ -158,8 +168,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) spmm_umma_kernel(const SpmmAr
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    if (warp >= 5) {  // gathered-row ids of the whole group, once
-        const int pt = tid - 160;
+    if (warp >= 7) {  // gathered-row ids of the whole group, once
+        const int pt = tid - 224;
         const int chunks = n_tiles * 2;
         for (int c = pt; c < chunks; c += 128) cp16(base + L::kIds + c * 16, p.val_sidx + (int64_t)t0 * kTileCols + c * 4);
         asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
@@ -169,9 +179,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) spmm_umma_kernel(const SpmmAr
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp >= 5) {
+    if (warp >= 7) {
         // ------------------------------ producers ------------------------------------------------
-        const int pw = warp - 5;                 // slab of this warp
+        const int pw = warp - 7;                 // slab of this warp
         const int lr = lane >> 3, lc = lane & 7; // row (and row + 4), 16-byte chunk
         const uint32_t off0 = (uint32_t)(lr * 128 + ((lc ^ (2 * lr)) * 16));   // 32-byte chunks swizzled by row % 4
         const uint32_t off1 = off0 + 512;                                     // row + 4: same swizzle phase
@@ -196,27 +206,39 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) spmm_umma_kernel(const SpmmAr
             if (++s == kUmmaStages) { s = 0; round++; }
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
-    } else if (warp == 4) {
-        // ------------------------------ MMA issuer -----------------------------------------------
-        int s = 0;
-        uint32_t round = 0, uses[2] = {0, 0};
-        int buf = 0;
-        bool ok = true;
-        for (int f = f0; f < f_end && ok; f++) {
-            const int n = p.frag_off[f + 1] - p.frag_off[f];
-            if (n == 0) continue;
-            if (uses[buf] > 0 && !mbar_wait(acce_bar(buf), (uses[buf] - 1) & 1, abort_flag)) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            for (int i = 0; i < n; i++) {
-                if (!mbar_wait(full_bar(s), round & 1, abort_flag)) { ok = false; break; }
-                // round the tile values to TF32 (nearest, ties away) in place
+    } else if (warp >= 5) {
+        // ------------------------------ prepare (two warps, alternate tiles) -------------------------
+        const int q = warp - 5;
+        for (int rel = q; rel < n_tiles; rel += 2) {
+            const int s = rel % kUmmaStages;
+            const uint32_t round = (uint32_t)(rel / kUmmaStages);
+            if (!mbar_wait(full_bar(s), round & 1, abort_flag)) break;
+            if (!(p.hints & 4)) {  // round the tile values to TF32 (nearest, ties away) in place
                 uint4* at = reinterpret_cast<uint4*>(gbase + L::kA + s * kUmmaABytes) + lane;
                 uint4 v = *at;
                 v.x += 0x1000u; v.y += 0x1000u; v.z += 0x1000u; v.w += 0x1000u;
                 *at = v;
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) {
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(ready_bar(s));
+        }
+    } else if (warp == 4) {
+        // ------------------------------ MMA issuer (one lane) ------------------------------------------
+        if (lane == 0) {
+            int s = 0;
+            uint32_t round = 0, uses0 = 0, uses1 = 0;
+            int buf = 0;
+            bool ok = true;
+            for (int f = f0; f < f_end && ok; f++) {
+                const int n = p.frag_off[f + 1] - p.frag_off[f];
+                if (n == 0) continue;
+                const uint32_t uses = buf ? uses1 : uses0;
+                if (uses > 0 && !mbar_wait(acce_bar(buf), (uses - 1) & 1, abort_flag)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int i = 0; i < n; i++) {
+                    if (!mbar_wait(ready_bar(s), round & 1, abort_flag)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t bdesc = umma_smem_desc(base + L::kA + s * kUmmaABytes, 1, 16, kSwizzle32B);
 #pragma unroll
                     for (int slab = 0; slab < kUmmaSlabs; slab++) {
@@ -224,16 +246,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) spmm_umma_kernel(const SpmmAr
                         umma_tf32(tmem_base + buf * 64 + slab * 16, adesc, bdesc, i > 0 ? 1u : 0u);
                     }
                     umma_commit(empty_bar(s));   // the slot is free once these MMAs have read it
+                    if (++s == kUmmaStages) { s = 0; round++; }
                 }
-                __syncwarp();
-                if (++s == kUmmaStages) { s = 0; round++; }
+                if (!ok) break;
+                umma_commit(accf_bar(buf));      // accumulators of this fragment complete
+                if (buf) uses1++; else uses0++;
+                buf ^= 1;
             }
-            if (!ok) break;
-            if (lane == 0) umma_commit(accf_bar(buf));  // accumulators of this fragment complete
-            __syncwarp();
-            uses[buf]++;
-            buf ^= 1;
         }
+        __syncwarp();
     } else {
         // ------------------------------ epilogue -------------------------------------------------
         uint32_t uses[2] = {0, 0};
