@@ -141,8 +141,8 @@ def panel_bounds(m, parts: int, dev) -> list[int]:
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the dominant kernel,
 # captured once with ncu on exactly this workload on one GPU; keyed by (workload, scale, N, format).
 NCU_TRAFFIC_BYTES = {
-    ("rmat20_gcn", None, 512, "srbcrs"): 17.31e9 + 2.33e9,   # profiles/spmm_async_kernel_rmat_n512.md
-    ("rmat20_gcn", 18, 512, "srbcrs"): 2.559e9 + 0.547e9,
+    ("rmat20_gcn", None, 512, "srbcrs"): 17.27e9 + 2.21e9,   # profiles/spmm_umma_kernel_n512.md
+    ("rmat20_gcn", 18, 512, "srbcrs"): 2.616e9 + 0.558e9,
 }
 
 
@@ -253,7 +253,7 @@ def main():
     ap.add_argument("--policy", default="auto")
     ap.add_argument("--group-tiles", type=int, default=0)
     ap.add_argument("--hints", type=int, default=0, help="kernel variant: L2 eviction hints bitmask")
-    ap.add_argument("--umma", type=int, default=0, help="1 = tcgen05 / tensor-memory kernel")
+    ap.add_argument("--umma", type=int, default=1, help="1 = tcgen05 / tensor-memory kernel where it applies, 0 = mma.sync kernels")
     ap.add_argument("--e2e-steps", type=int, default=3, help="0 skips the host-buffer leg")
     ap.add_argument("--nq", type=int, default=0, help="kernel variant: 32-column groups per warp (0 = default)")
     ap.add_argument("--min-blocks", type=int, default=0, help="kernel variant: occupancy target (0 = default)")
@@ -326,6 +326,9 @@ def main():
         torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
+    kernel_status = plan.status()
+    if kernel_status != 0:
+        raise RuntimeError("a kernel gave up on a bounded wait during the timed region; the result is invalid")
     total_ms = ev[0].elapsed_time(ev[-1])
     per_launch = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
     t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
@@ -408,7 +411,7 @@ def main():
     roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
                 "traffic": NCU_TRAFFIC_BYTES.get((args.workload, args.scale, N, args.format)) if world == 1 else None,
                 "peak_source": peak_src, "bytes_algorithmic": bytes_alg,
-                "kernel_ms": kernel_ms, "kernel": "spmm_async_kernel (+ spmm_fixup_kernel)",
+                "kernel_ms": kernel_ms, "kernel": ("spmm_umma_kernel" if (args.umma and N % 512 == 0 and args.format == "srbcrs") else "spmm_async_kernel") + " (+ spmm_fixup_kernel)",
                 "bytes_gather_no_reuse": bytes_alg - 4 * N * distinct + 4 * N * G_rows,
                 "padded_tile_tflop": 256.0 * packed.T * N / 1e12,
                 "tf32_dense_peak_tflops_measured": tf32_tflops,
@@ -458,7 +461,7 @@ def main():
                        "partition": "tile-balanced row panels on window boundaries, B replicated" if world > 1 else "none",
                        "l2": "no flush needed: B and C (M*N*4 bytes each) are far larger than the 126 MB L2"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
-            "clocks": clocks.summary(), "verified": verified,
+            "clocks": clocks.summary(), "verified": verified, "kernel_status": kernel_status,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

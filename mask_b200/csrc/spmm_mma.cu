@@ -41,7 +41,7 @@ static int g_tune_min_blocks = 0;
 static int g_tune_async = 1;   // 1 = shared-memory ring fed by cp.async (SR-BCRS), 0 = register pipeline
 static int g_tune_stages = 0;
 static int g_tune_hints = 0;
-static int g_tune_umma = 0;    // 1 = tcgen05 kernel where it applies
+static int g_tune_umma = 1;    // 1 = tcgen05 kernel where it applies (SR-BCRS, N % 512 == 0, groups <= 256 tiles)
 
 template <int NQ, bool METCF, int MIN_BLOCKS>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, MIN_BLOCKS) spmm_mma_kernel(const SpmmArgs p) {

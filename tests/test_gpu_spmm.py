@@ -95,12 +95,14 @@ def test_srbcrs_spmm_kernel_variants(oracle_mod, name, N, use_async, nq, knob):
     p = engine.pack_srbcrs(rp, ci, va, m.M, m.K)
     B = _dense(m.K, N, 9)
     try:
+        engine.tune("umma", 0)
         engine.tune("async", use_async)
         engine.tune("nq", nq)
         engine.tune("stages" if use_async else "min_blocks", knob)
         out = torch.full((m.M, N), float("nan"), device="cuda")
         engine.spmm(p, torch.from_numpy(B).cuda(), out=out, plan=engine.Plan(p.val_soff, m.M, p.T, "auto", 3))
     finally:
+        engine.tune("umma", 1)
         engine.tune("async", 1)
         engine.tune("nq", 0)
         engine.tune("stages", 0)
@@ -239,7 +241,7 @@ def test_srbcrs_spmm_tcgen05_kernel(oracle_mod, name, N, gt):
         out2 = torch.full((m.M, N), float("nan"), device="cuda")
         engine.spmm(p, Bd, out=out2, plan=plan, relu=True)
     finally:
-        engine.tune("umma", 0)
+        engine.tune("umma", 1)
     assert plan.status() == 0
     _assert_close(oracle_mod, m, B, out.cpu().numpy())
     assert torch.equal(torch.relu(out), out2)
