@@ -92,6 +92,29 @@ int mask_metcf_fill(const int32_t* d_rowptr, const int32_t* d_colind, const floa
                     float* d_val_coo_val, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Row reorders of the Format-DSL host bridge (examples/src_fp32/acc/testbed/custom_format_e2e.cu:
+ * 163-347): reverse_cuthill_mckee, first_column_order, jaccard_greedy_order, with the same
+ * tie-breaks, so the orders are bit-identical.  h_row_order[new_row] = original_row.  Host
+ * functions (the bridge computes them on the host too, outside its timed region).
+ * ------------------------------------------------------------------------------------------ */
+typedef enum mask_reorder {
+    MASK_REORDER_NONE = 0,
+    MASK_REORDER_ROW_RCM = 1,        /* square matrices only */
+    MASK_REORDER_FIRST_COL_SORT = 2,
+    MASK_REORDER_JACCARD_GREEDY = 3
+} mask_reorder;
+
+int mask_reorder_rows(int kind, const int32_t* h_rowptr, const int32_t* h_colind, int32_t M,
+                      int32_t K, int32_t* h_row_order);
+
+/* Applies an order on the device: row i of the output CSR is row d_row_order[i] of the input
+ * (what the bridge's packer does while walking row_order, custom_format_e2e.cu:554-568).
+ * d_rowptr_out has M+1 entries; the colind / values pairs may be NULL to get row pointers only. */
+int mask_csr_permute_rows(const int32_t* d_rowptr, const int32_t* d_colind, const float* d_values,
+                          int32_t M, const int32_t* d_row_order, int32_t* d_rowptr_out,
+                          int32_t* d_colind_out, float* d_values_out, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Task planners (host, pure functions).  Bit-identical to strict_load_balance
  * (examples/src_fp32/sr_bcrs/testbed/main_strict_lb_16x8.cu:208-256) and
  * multi_binding_load_balance (examples/src_fp32/sr_bcrs/testbed/main_multi_bind_16x8.cu:207-271).
@@ -134,6 +157,11 @@ size_t mask_plan_scratch_bytes(const mask_plan* plan, int32_t N);
 /* Introspection for tests: numbers of fragments, groups, split fragments, and the group size. */
 int mask_plan_info(const mask_plan* plan, int64_t* n_frag, int64_t* n_groups, int64_t* n_partial,
                    int32_t* group_tiles);
+/* Makes every SpMM launched with this plan write packed row i to output row d_row_order[i]
+ * (NULL = identity): a matrix packed from reordered rows then produces C in the original row
+ * order with no separate pass.  Replaces the bridge's host-side unpack_output
+ * (custom_format_e2e.cu:1083-1100).  The array (M entries) is not owned by the plan. */
+int mask_plan_set_row_map(mask_plan* plan, const int32_t* d_row_order);
 /* Reads the plan's device status word (synchronises): 0, or non-zero if a kernel launched with
  * this plan gave up on one of its bounded waits (its output is then invalid).  No counterpart in
  * the reference, whose kernels have no waits. */

@@ -23,6 +23,9 @@ SIGNATURES = {
     "mask_srbcrs_fill": (C.c_int, [vp, vp, vp, i32, i64, vp, vp, i64, vp, vp, vp, vp, vp, vp]),
     "mask_metcf_offsets": (C.c_int, [vp, i32, i64, vp, vp, i64, vp, vp, C.POINTER(i64), vp]),
     "mask_metcf_fill": (C.c_int, [vp, vp, vp, i32, i64, vp, vp, i64, vp, vp, i64, vp, vp, vp, vp]),
+    "mask_reorder_rows": (C.c_int, [C.c_int, vp, vp, i32, i32, vp]),
+    "mask_csr_permute_rows": (C.c_int, [vp, vp, vp, i32, vp, vp, vp, vp, vp]),
+    "mask_plan_set_row_map": (C.c_int, [vp, vp]),
     "mask_plan_strict_lb": (C.c_int, [vp, i32, i32, vp, vp, vp, C.POINTER(i64), C.POINTER(i64)]),
     "mask_plan_multi_bind": (C.c_int, [vp, i32, vp, vp, vp, C.POINTER(i64)]),
     "mask_plan_create": (C.c_int, [vp, i32, i64, C.c_int, i32, vp, C.POINTER(vp)]),
@@ -43,6 +46,7 @@ SIGNATURES = {
     "mask_session_destroy": (None, [vp]),
 }
 
+REORDER = {"none": 0, "row_rcm": 1, "first_col_sort": 2, "jaccard_greedy": 3}
 POLICY = {"auto": 0, "row": 1, "strict_lb": 2, "multi_bind": 3}
 EPILOGUE_NONE, EPILOGUE_RELU = 0, 1
 

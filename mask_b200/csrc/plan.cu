@@ -277,6 +277,13 @@ extern "C" int mask_plan_info(const mask_plan* p, int64_t* n_frag, int64_t* n_gr
     return MASK_OK;
 }
 
+extern "C" int mask_plan_set_row_map(mask_plan* p, const int32_t* d_row_order) {
+    using namespace mask;
+    MASK_REQUIRE(p != nullptr, "plan is NULL");
+    p->d_row_map = d_row_order;
+    return MASK_OK;
+}
+
 extern "C" int mask_plan_status(const mask_plan* p, int32_t* h_status, void* stream) {
     using namespace mask;
     MASK_REQUIRE(p != nullptr && h_status != nullptr, "NULL argument");

@@ -29,5 +29,6 @@ struct mask_plan {
     int32_t* d_frag_slot = nullptr;
     int32_t* d_group_off = nullptr;
     int32_t* d_head_frag = nullptr;
+    const int32_t* d_row_map = nullptr;  // optional, not owned: output row of packed row i (a row reorder's order[])
     int32_t* d_status = nullptr;  // device status word: non-zero after a kernel gave up on a bounded wait
 };

@@ -16,6 +16,7 @@ struct SpmmArgs {
     const int32_t* coo_off;    // ME-TCF
     const int32_t* coo_idx;
     const float* coo_val;
+    const int32_t* row_map;    // optional: packed row i is output row row_map[i] (row reorder undone on the fly)
     const float* B;
     int64_t ldb;
     float* C;
@@ -89,7 +90,7 @@ __device__ __forceinline__ void flush_fragment(const SpmmArgs& p, int ff, int co
                 v1.x = fmaxf(v1.x, 0.f); v1.y = fmaxf(v1.y, 0.f); v1.z = fmaxf(v1.z, 0.f); v1.w = fmaxf(v1.w, 0.f);
             }
             if (r < rows_ok) {
-                float* row = dst + (int64_t)r * ld;
+                float* row = (slot < 0 && p.row_map) ? p.C + (int64_t)p.row_map[w * kWinRows + r] * p.ldc : dst + (int64_t)r * ld;
                 if (p.hints & 2) {  // C is written once and not read again by this kernel
                     if (c0 < p.N) __stcs(reinterpret_cast<float4*>(row + c0), v0);
                     if (c0 + 4 < p.N) __stcs(reinterpret_cast<float4*>(row + c0 + 4), v1);

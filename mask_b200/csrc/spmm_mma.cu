@@ -239,7 +239,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, MIN_BLOCKS) spmm_mma_kern
 __global__ void __launch_bounds__(256) spmm_fixup_kernel(const int32_t* head_frag, const int32_t* frag_win,
                                                         const int32_t* frag_slot, int64_t n_frag,
                                                         const float* scratch, float* C, int64_t ldc, int32_t M,
-                                                        int32_t N, int32_t relu) {
+                                                        int32_t N, int32_t relu, const int32_t* row_map) {
     const int64_t f0 = head_frag[blockIdx.x];
     const int w = frag_win[f0];
     int64_t f1 = f0;
@@ -254,7 +254,8 @@ __global__ void __launch_bounds__(256) spmm_fixup_kernel(const int32_t* head_fra
             s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
         }
         if (relu) { s.x = fmaxf(s.x, 0.f); s.y = fmaxf(s.y, 0.f); s.z = fmaxf(s.z, 0.f); s.w = fmaxf(s.w, 0.f); }
-        *reinterpret_cast<float4*>(C + (int64_t)(w * kWinRows + r) * ldc + c) = s;
+        const int out_row = row_map ? row_map[w * kWinRows + r] : w * kWinRows + r;
+        *reinterpret_cast<float4*>(C + (int64_t)out_row * ldc + c) = s;
     }
 }
 
@@ -262,7 +263,7 @@ static int launch_fixup(const mask_plan* plan, const SpmmArgs& a, cudaStream_t s
     if (plan->H > 0) {
         dim3 fgrid((unsigned)plan->H, (unsigned)((kWinRows * (a.N >> 2) + 255) / 256));
         spmm_fixup_kernel<<<fgrid, 256, 0, st>>>(plan->d_head_frag, plan->d_frag_win, plan->d_frag_slot, plan->F,
-                                                 a.scratch, a.C, a.ldc, a.M, a.N, a.relu);
+                                                 a.scratch, a.C, a.ldc, a.M, a.N, a.relu, a.row_map);
         MASK_CUDA_TRY(cudaGetLastError());
     }
     return MASK_OK;
@@ -275,6 +276,7 @@ static int launch_spmm(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
     a.frag_win = plan->d_frag_win;
     a.frag_slot = plan->d_frag_slot;
     a.group_off = plan->d_group_off;
+    a.row_map = plan->d_row_map;
     // columns per warp: wide slabs (fewer re-reads of the tile values per column) when N fills
     // four warps of them, else narrower slabs so that small N still spreads over a block
     const int N = a.N;

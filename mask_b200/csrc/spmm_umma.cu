@@ -293,11 +293,12 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) spmm_umma_kernel(const SpmmAr
             for (int i = 0; i < 16; i++) {
                 const int r = i ^ (i >> 3);   // MMA-N index -> window row (rows 8..15 swapped pairwise)
                 if (r < rows_ok) {
+                    float* row = (slot < 0 && p.row_map) ? p.C + (int64_t)p.row_map[w * kWinRows + r] * p.ldc : dst + (int64_t)r * ld;
 #pragma unroll
                     for (int sl = 0; sl < kUmmaSlabs; sl++) {
                         float x = __uint_as_float(v[sl][i]);
                         if (relu) x = fmaxf(x, 0.f);
-                        dst[(int64_t)r * ld + col + 128 * sl] = x;
+                        row[col + 128 * sl] = x;
                     }
                 }
             }

@@ -97,13 +97,22 @@ class PackedSRBCRS:
     block_partition: torch.Tensor | None = None
     edge_to_col: torch.Tensor | None = None
     edge_to_row: torch.Tensor | None = None
+    row_order: torch.Tensor | None = None   # set when the rows were reordered: packed row i = original row row_order[i]
     plans: dict = field(default_factory=dict)
 
     def plan(self, policy: str = "auto", group_tiles: int = 0) -> Plan:
         key = (policy, group_tiles)
         if key not in self.plans:
-            self.plans[key] = Plan(self.val_soff, self.M, self.T, policy, group_tiles)
+            self.plans[key] = self.new_plan(policy, group_tiles)
         return self.plans[key]
+
+    def new_plan(self, policy: str = "auto", group_tiles: int = 0) -> Plan:
+        """A plan for this matrix; carries the row map when the rows were reordered."""
+        p = Plan(self.val_soff, self.M, self.T, policy, group_tiles)
+        if self.row_order is not None:
+            check(lib().mask_plan_set_row_map(p._h, _ptr(self.row_order)), "mask_plan_set_row_map")
+            p._row_order = self.row_order  # keep the array alive as long as the plan
+        return p
 
 
 @dataclass
@@ -119,9 +128,11 @@ class PackedMETCF:
     val_coo_off: torch.Tensor
     val_coo_idx: torch.Tensor
     val_coo_val: torch.Tensor
+    row_order: torch.Tensor | None = None
     plans: dict = field(default_factory=dict)
 
     plan = PackedSRBCRS.plan
+    new_plan = PackedSRBCRS.new_plan
 
 
 def _analyze(rowptr, colind, M, K):
@@ -144,11 +155,40 @@ def _analyze(rowptr, colind, M, K):
     return ws, val_soff, int(T.value), nnz
 
 
-def pack_srbcrs(rowptr, colind, values, M: int, K: int, side_outputs: bool = False) -> PackedSRBCRS:
-    """CSR (device, rows strictly ascending) -> SR-BCRS 16x8 on the device."""
+def reorder_rows(rowptr, colind, M: int, K: int, kind: str) -> torch.Tensor:
+    """Row order of one of the Format-DSL bridge's reorders (``row_rcm``, ``first_col_sort``,
+    ``jaccard_greedy``), computed on the host like the bridge does; returns order[new] = original
+    as an int32 tensor on the CSR's device."""
+    _req(rowptr, torch.int32, "rowptr")
+    _req(colind, torch.int32, "colind")
+    rp, ci = rowptr.cpu(), colind.cpu()
+    order = torch.empty(M, dtype=torch.int32)
+    check(lib().mask_reorder_rows(_lib.REORDER[kind], _ptr(rp), _ptr(ci), M, K, _ptr(order)), "mask_reorder_rows")
+    return order.to(rowptr.device)
+
+
+def permute_rows(rowptr, colind, values, M: int, order: torch.Tensor):
+    """Device CSR whose row i is row order[i] of the input."""
+    _req(order, torch.int32, "order")
+    rp = torch.empty_like(rowptr)
+    ci = torch.empty_like(colind)
+    va = torch.empty_like(values)
+    check(lib().mask_csr_permute_rows(_ptr(rowptr), _ptr(colind), _ptr(values), M, _ptr(order), _ptr(rp), _ptr(ci),
+                                      _ptr(va), _stream()), "mask_csr_permute_rows")
+    return rp, ci, va
+
+
+def pack_srbcrs(rowptr, colind, values, M: int, K: int, side_outputs: bool = False, reorder: str = "none") -> PackedSRBCRS:
+    """CSR (device, rows strictly ascending) -> SR-BCRS 16x8 on the device.  With ``reorder`` the
+    rows are packed in that order and products still come back in the original row order."""
     _req(values, torch.float32, "values")
     if values.numel() != colind.numel():
         raise RuntimeError("values length must equal colind length")
+    if reorder != "none":
+        order = reorder_rows(rowptr, colind, M, K, reorder)
+        packed = pack_srbcrs(*permute_rows(rowptr, colind, values, M, order), M, K, side_outputs)
+        packed.row_order = order
+        return packed
     ws, val_soff, T, nnz = _analyze(rowptr, colind, M, K)
     dev = rowptr.device
     val_sidx = torch.empty(8 * T, dtype=torch.int32, device=dev)
@@ -204,6 +244,8 @@ def spmm(packed, dense: torch.Tensor, out: torch.Tensor | None = None, policy: s
     if N == 0:
         return out
     plan = plan or packed.plan(policy)
+    if packed.row_order is not None and getattr(plan, "_row_order", None) is not packed.row_order:
+        raise RuntimeError("this matrix was packed from reordered rows: use packed.plan() / packed.new_plan()")
     scratch = plan.scratch(N, dense.device)
     sb = 0 if scratch is None else scratch.numel()
     epi = _lib.EPILOGUE_RELU if relu else _lib.EPILOGUE_NONE

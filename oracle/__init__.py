@@ -65,6 +65,14 @@ def lib() -> C.CDLL:
         L.oracle_check_tolerance.restype = C.c_int64
         L.oracle_check_tolerance.argtypes = [C.c_int64, C.c_int, _f32p, C.c_int64, _f32p, C.c_int64, _f64p,
                                              C.c_int64, C.c_double, C.c_double, C.POINTER(C.c_double)]
+        L.oracle_reorder_first_col.restype = None
+        L.oracle_reorder_first_col.argtypes = [C.c_int, C.c_int, _i32p, _i32p, _i32p]
+        L.oracle_reorder_rcm.restype = C.c_int
+        L.oracle_reorder_rcm.argtypes = [C.c_int, C.c_int, _i32p, _i32p, _i32p]
+        L.oracle_reorder_jaccard.restype = None
+        L.oracle_reorder_jaccard.argtypes = [C.c_int, C.c_int, _i32p, _i32p, _i32p]
+        L.oracle_permute_csr.restype = None
+        L.oracle_permute_csr.argtypes = [C.c_int, _i32p, _i32p, _f32p, _i32p, _i32p, _i32p, _f32p]
         L.oracle_max_threads.restype = C.c_int
         L.oracle_rna_tf32.restype = C.c_float
         L.oracle_rna_tf32.argtypes = [C.c_float]
@@ -152,6 +160,47 @@ def multi_bind_plan(M, val_soff):
     return tw[:P], ws[:W], ts
 
 
+REORDER_KINDS = {"row_rcm": 1, "first_col_sort": 2, "jaccard_greedy": 3}
+
+
+def reorder_rows(kind, M, K, rowptr, colind):
+    """row_order[new_row] = original_row for one of the bridge's three reorders."""
+    L = lib()
+    rowptr, colind = _c(rowptr, np.int32), _c(colind, np.int32)
+    order = np.zeros(M, dtype=np.int32)
+    if kind == "first_col_sort":
+        L.oracle_reorder_first_col(M, K, rowptr, colind, order)
+    elif kind == "row_rcm":
+        if L.oracle_reorder_rcm(M, K, rowptr, colind, order) != 0:
+            raise ValueError("row_rcm needs a square matrix")
+    elif kind == "jaccard_greedy":
+        L.oracle_reorder_jaccard(M, K, rowptr, colind, order)
+    else:
+        raise ValueError(kind)
+    return order
+
+
+def permute_csr(M, rowptr, colind, values, order):
+    L = lib()
+    rowptr, colind, values = _c(rowptr, np.int32), _c(colind, np.int32), _c(values, np.float32)
+    rp = np.zeros(M + 1, dtype=np.int32)
+    ci = np.zeros_like(colind)
+    va = np.zeros_like(values)
+    L.oracle_permute_csr(M, rowptr, colind, values, _c(order, np.int32), rp, ci, va)
+    return rp, ci, va
+
+
+def ref_reorder_rows(kind, M, K, rowptr, colind):
+    R = _ref("libref_bridge.so")
+    R.ref_reorder_rows.restype = C.c_int
+    R.ref_reorder_rows.argtypes = [C.c_int, C.c_int, C.c_int, _i32p, _i32p, _i32p]
+    order = np.zeros(M, dtype=np.int32)
+    rc = R.ref_reorder_rows(REORDER_KINDS[kind], M, K, _c(rowptr, np.int32), _c(colind, np.int32), order)
+    if rc != 0:
+        raise ValueError(f"reference reorder failed ({rc})")
+    return order
+
+
 def max_threads() -> int:
     return int(lib().oracle_max_threads())
 
@@ -219,7 +268,8 @@ def check_tolerance(got, ref, absprod, rtol=RTOL, atol=ATOL):
 
 def ref_available() -> bool:
     return all(os.path.exists(os.path.join(_HERE, "_ref", n)) for n in
-               ("libref_srbcrs.so", "libref_strict_lb.so", "libref_multi_bind.so", "libref_metcf.so"))
+               ("libref_srbcrs.so", "libref_strict_lb.so", "libref_multi_bind.so", "libref_metcf.so",
+                "libref_bridge.so"))
 
 
 def _ref(name):

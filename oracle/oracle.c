@@ -9,7 +9,7 @@
  *
  * Parity status: PINNED.  Every packer / planner below is compared byte for byte against the
  * reference project's own host code (built from the reference sources into oracle/_ref by
- * oracle/Makefile) in tests/test_oracle_vs_reference.py, and against the committed fixtures
+ * oracle/Makefile) in tests/test_oracle.py, and against the committed fixtures
  * under tests/golden/ that were generated from those reference builds.
  *
  * Citations are paths inside the reference project.
@@ -449,4 +449,180 @@ int64_t oracle_check_tolerance(int64_t rows, int N, const float* got, int64_t ld
     }
     *worst_ratio = worst;
     return bad;
+}
+
+/* ---- row reorders of the Format-DSL host bridge ------------------------------------------------
+ * Restated from examples/src_fp32/acc/testbed/custom_format_e2e.cu:163-347.  Each returns
+ * row_order[new_row] = original_row.  Deterministic tie-breaks are part of the contract. */
+
+static const int* g_sort_key_a;
+
+static const uint64_t* g_sort_key_u;
+static int cmp_key_a_then_id(const void* x, const void* y) {
+    int l = *(const int*)x, r = *(const int*)y;
+    if (g_sort_key_a[l] != g_sort_key_a[r]) return g_sort_key_a[l] < g_sort_key_a[r] ? -1 : 1;
+    return (l > r) - (l < r);
+}
+static int cmp_u_a_then_id(const void* x, const void* y) {
+    int l = *(const int*)x, r = *(const int*)y;
+    if (g_sort_key_u[l] != g_sort_key_u[r]) return g_sort_key_u[l] < g_sort_key_u[r] ? -1 : 1;
+    if (g_sort_key_a[l] != g_sort_key_a[r]) return g_sort_key_a[l] < g_sort_key_a[r] ? -1 : 1;
+    return (l > r) - (l < r);
+}
+
+static int first_col(int row, int K, const int* rowptr, const int* colind) {
+    int first = K;
+    for (int p = rowptr[row]; p < rowptr[row + 1]; p++)
+        if (colind[p] >= 0 && colind[p] < K && colind[p] < first) first = colind[p];
+    return first;
+}
+
+/* first_col_sort (custom_format_e2e.cu:233-255): stable order by (first structural column, row). */
+void oracle_reorder_first_col(int M, int K, const int* rowptr, const int* colind, int* order) {
+    int* first = (int*)malloc(sizeof(int) * (size_t)(M > 0 ? M : 1));
+    for (int r = 0; r < M; r++) { first[r] = first_col(r, K, rowptr, colind); order[r] = r; }
+    g_sort_key_a = first;
+    qsort(order, (size_t)M, sizeof(int), cmp_key_a_then_id);  /* total order: ties broken by id */
+    free(first);
+}
+
+/* row_rcm (custom_format_e2e.cu:163-231): reverse Cuthill-McKee on the symmetrised structure;
+ * components started from the unvisited row of least (degree, id); neighbours enqueued in
+ * (degree, id) order; every component reversed.  Square matrices only; returns 0 on success. */
+int oracle_reorder_rcm(int M, int K, const int* rowptr, const int* colind, int* order) {
+    if (M != K) return 1;
+    int64_t* cnt = (int64_t*)calloc((size_t)M + 1, sizeof(int64_t));
+    for (int r = 0; r < M; r++)
+        for (int p = rowptr[r]; p < rowptr[r + 1]; p++) {
+            int c = colind[p];
+            if (c < 0 || c >= M || c == r) continue;
+            cnt[r + 1]++; cnt[c + 1]++;
+        }
+    for (int r = 0; r < M; r++) cnt[r + 1] += cnt[r];
+    int* adj = (int*)malloc(sizeof(int) * (size_t)(cnt[M] > 0 ? cnt[M] : 1));
+    int64_t* fill = (int64_t*)malloc(sizeof(int64_t) * (size_t)(M > 0 ? M : 1));
+    for (int r = 0; r < M; r++) fill[r] = cnt[r];
+    for (int r = 0; r < M; r++)
+        for (int p = rowptr[r]; p < rowptr[r + 1]; p++) {
+            int c = colind[p];
+            if (c < 0 || c >= M || c == r) continue;
+            adj[fill[r]++] = c; adj[fill[c]++] = r;
+        }
+    int64_t* abeg = (int64_t*)malloc(sizeof(int64_t) * (size_t)(M + 1));
+    int* degree = (int*)malloc(sizeof(int) * (size_t)(M > 0 ? M : 1));
+    for (int r = 0; r < M; r++) {  /* sort + unique each neighbour list */
+        int* a = adj + cnt[r];
+        int n = (int)(cnt[r + 1] - cnt[r]);
+        qsort(a, (size_t)n, sizeof(int), cmp_int);
+        int u = 0;
+        for (int i = 0; i < n; i++) if (i == 0 || a[i] != a[u - 1]) a[u++] = a[i];
+        degree[r] = u;
+        abeg[r] = cnt[r];
+    }
+    int* starts = (int*)malloc(sizeof(int) * (size_t)(M > 0 ? M : 1));
+    for (int r = 0; r < M; r++) starts[r] = r;
+    g_sort_key_a = degree;
+    qsort(starts, (size_t)M, sizeof(int), cmp_key_a_then_id);
+    unsigned char* visited = (unsigned char*)calloc((size_t)(M > 0 ? M : 1), 1);
+    int* queue = (int*)malloc(sizeof(int) * (size_t)(M > 0 ? M : 1));
+    int* next = (int*)malloc(sizeof(int) * (size_t)(M > 0 ? M : 1));
+    int out = 0;
+    for (int si = 0; si < M; si++) {
+        int start = starts[si];
+        if (visited[start]) continue;
+        int qh = 0, qt = 0, comp_begin = out;
+        visited[start] = 1;
+        queue[qt++] = start;
+        while (qh < qt) {
+            int row = queue[qh++];
+            order[out++] = row;
+            int nn = 0;
+            for (int i = 0; i < degree[row]; i++) {
+                int nb = adj[abeg[row] + i];
+                if (!visited[nb]) next[nn++] = nb;
+            }
+            qsort(next, (size_t)nn, sizeof(int), cmp_key_a_then_id);
+            for (int i = 0; i < nn; i++)
+                if (!visited[next[i]]) { visited[next[i]] = 1; queue[qt++] = next[i]; }
+        }
+        for (int i = comp_begin, j = out - 1; i < j; i++, j--) { int t = order[i]; order[i] = order[j]; order[j] = t; }
+    }
+    free(cnt); free(adj); free(fill); free(abeg); free(degree); free(starts); free(visited); free(queue); free(next);
+    return out == M ? 0 : 2;
+}
+
+static uint64_t mix_column(uint64_t v) {
+    v += 0x9e3779b97f4a7c15ULL;
+    v = (v ^ (v >> 30)) * 0xbf58476d1ce4e5b9ULL;
+    v = (v ^ (v >> 27)) * 0x94d049bb133111ebULL;
+    return v ^ (v >> 31);
+}
+
+static double row_jaccard(int l, int r, const int* rowptr, const int* colind) {
+    int a = rowptr[l], b = rowptr[r];
+    const int ae = rowptr[l + 1], be = rowptr[r + 1];
+    int inter = 0, lu = 0, ru = 0;
+    while (a < ae || b < be) {
+        const int lc = a < ae ? colind[a] : 2147483647, rc = b < be ? colind[b] : 2147483647;
+        if (lc == rc) { inter++; lu++; ru++; while (a < ae && colind[a] == lc) a++; while (b < be && colind[b] == rc) b++; }
+        else if (lc < rc) { lu++; while (a < ae && colind[a] == lc) a++; }
+        else { ru++; while (b < be && colind[b] == rc) b++; }
+    }
+    const int uni = lu + ru - inter;
+    return uni ? (double)inter / uni : 1.0;
+}
+
+/* jaccard_greedy (custom_format_e2e.cu:257-347): rows ranked by (min-hash of their columns, first
+ * column, id), cut into buckets of 64 consecutive ranks; inside a bucket, starting from its first
+ * row, repeatedly append the remaining row with the largest exact Jaccard similarity to the row
+ * appended last (ties: smaller row id). */
+void oracle_reorder_jaccard(int M, int K, const int* rowptr, const int* colind, int* order) {
+    uint64_t* sig = (uint64_t*)malloc(sizeof(uint64_t) * (size_t)(M > 0 ? M : 1));
+    int* first = (int*)malloc(sizeof(int) * (size_t)(M > 0 ? M : 1));
+    int* ranked = (int*)malloc(sizeof(int) * (size_t)(M > 0 ? M : 1));
+    for (int r = 0; r < M; r++) {
+        uint64_t s = UINT64_MAX;
+        for (int p = rowptr[r]; p < rowptr[r + 1]; p++) {
+            uint64_t h = mix_column((uint64_t)(uint32_t)colind[p]);
+            if (h < s) s = h;
+        }
+        sig[r] = s; first[r] = first_col(r, K, rowptr, colind); ranked[r] = r;
+    }
+    g_sort_key_u = sig; g_sort_key_a = first;
+    qsort(ranked, (size_t)M, sizeof(int), cmp_u_a_then_id);
+    int out = 0;
+    int rem[64];
+    for (int base = 0; base < M; base += 64) {
+        int n = M - base < 64 ? M - base : 64;
+        memcpy(rem, ranked + base, sizeof(int) * (size_t)n);
+        int cur = rem[0];
+        order[out++] = cur;
+        memmove(rem, rem + 1, sizeof(int) * (size_t)(--n));
+        while (n > 0) {
+            int best = 0;
+            double best_score = -1.0;
+            for (int c = 0; c < n; c++) {
+                double s = row_jaccard(cur, rem[c], rowptr, colind);
+                if (s > best_score || (s == best_score && rem[c] < rem[best])) { best_score = s; best = c; }
+            }
+            cur = rem[best];
+            order[out++] = cur;
+            memmove(rem + best, rem + best + 1, sizeof(int) * (size_t)(n - best - 1));
+            n--;
+        }
+    }
+    free(sig); free(first); free(ranked);
+}
+
+/* Rows of a CSR matrix taken in `order` (new_row -> original_row): the input of the packers after
+ * a reorder (custom_format_e2e.cu:554-568 walks rows through row_order the same way). */
+void oracle_permute_csr(int M, const int* rowptr, const int* colind, const float* values, const int* order,
+                        int* rowptr_out, int* colind_out, float* values_out) {
+    rowptr_out[0] = 0;
+    for (int i = 0; i < M; i++) {
+        const int r = order[i], n = rowptr[r + 1] - rowptr[r];
+        memcpy(colind_out + rowptr_out[i], colind + rowptr[r], sizeof(int) * (size_t)n);
+        memcpy(values_out + rowptr_out[i], values + rowptr[r], sizeof(float) * (size_t)n);
+        rowptr_out[i + 1] = rowptr_out[i] + n;
+    }
 }

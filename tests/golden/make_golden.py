@@ -7,7 +7,8 @@ Run in a container that holds a checkout of the reference project (default /root
 
 Each fixture stores a small CSR matrix together with what the reference code produced for it:
 SR-BCRS 16x8 arrays (convertToSRBCRS), ME-TCF arrays (buildMETCFMetadata), the strict_lb tables
-for a group size of 64 and of 8 tiles, and the multi_bind tables.  The fixtures travel with the
+for a group size of 64 and of 8 tiles, the multi_bind tables, and the row orders of the Format-DSL
+bridge's reorders (first_col_sort, jaccard_greedy; row_rcm for square matrices).  The fixtures travel with the
 repository; the reference checkout does not.
 """
 import os
@@ -68,6 +69,8 @@ def main():
             out[f"slb{wl}_row_block_offset"] = rbo
             out[f"slb{wl}_row_block_to_window"] = rb2w
             out[f"slb{wl}_group_offset"] = go
+        for kind in ("first_col_sort", "jaccard_greedy") + (("row_rcm",) if m.M == m.K else ()):
+            out["order_" + kind] = oracle.ref_reorder_rows(kind, m.M, m.K, m.rowptr, m.colind)
         tw, ws, ts = oracle.ref_multi_bind_plan(m.M, sr["val_soff"])
         out.update(mb_task_window=tw, mb_window_split=ws, mb_task_soff=ts)
         path = os.path.join(HERE, name + ".npz")

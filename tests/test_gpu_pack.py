@@ -118,3 +118,33 @@ def test_plan_tables(oracle_mod):
                 rbo, rb2w, _ = oracle_mod.strict_lb_plan(m.M, soff, 8)
                 keep = np.diff(fo) > 0
                 assert np.array_equal(fo[:-1][keep], rbo[:-1]) and np.array_equal(fw[keep], rb2w)
+
+
+@pytest.mark.parametrize("kind", ["first_col_sort", "jaccard_greedy", "row_rcm"])
+@pytest.mark.parametrize("name", ["rmat10", "hub_rows", "m33_empty_window", "stencil8"])
+def test_reordered_pack_and_product(oracle_mod, name, kind):
+    """Rows reordered like the Format-DSL bridge: the packed arrays equal the oracle's pack of the
+    permuted CSR, and the product comes back in the original row order (row map in the epilogue)."""
+    import torch
+    from mask_b200 import engine, _lib
+    m = cases.SMALL[name]()
+    rp, ci, va = _dev(m)
+    if kind == "row_rcm" and m.M != m.K:
+        with pytest.raises(_lib.MaskError):
+            engine.pack_srbcrs(rp, ci, va, m.M, m.K, reorder=kind)
+        return
+    p = engine.pack_srbcrs(rp, ci, va, m.M, m.K, reorder=kind)
+    order = oracle_mod.reorder_rows(kind, m.M, m.K, m.rowptr, m.colind)
+    assert np.array_equal(p.row_order.cpu().numpy(), order)
+    prp, pci, pva = oracle_mod.permute_csr(m.M, m.rowptr, m.colind, m.values, order)
+    _check_srbcrs(p, oracle_mod.pack_srbcrs(m.M, prp, pci, pva))
+    for N, gt in ((512, 0), (96, 3)):   # tcgen05 kernel / mma.sync kernel with split windows
+        B = np.random.Generator(np.random.PCG64(N)).standard_normal((m.K, N), dtype=np.float32)
+        out = torch.full((m.M, N), float("nan"), device="cuda")
+        engine.spmm(p, torch.from_numpy(B).cuda(), out=out, plan=p.new_plan("auto", gt))
+        ref = oracle_mod.spmm_f32(m.M, m.rowptr, m.colind, m.values, B)
+        absp = oracle_mod.spmm_abs_f64(m.M, m.rowptr, m.colind, m.values, B)
+        bad, worst = oracle_mod.check_tolerance(out.cpu().numpy(), ref, absp)
+        assert bad == 0, worst
+    with pytest.raises(RuntimeError):
+        engine.spmm(p, torch.zeros((m.K, 16), device="cuda"), plan=engine.Plan(p.val_soff, m.M, p.T))

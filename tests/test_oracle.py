@@ -114,3 +114,23 @@ def test_generators_contract():
     assert np.array_equal(d, d.T)
     st = G.stencil27(grid=4)
     assert st.nnz == (3 * 4 - 2) ** 3  # sum over the grid of the truncated neighbourhood sizes
+
+
+@pytest.mark.parametrize("name", cases.golden_names())
+def test_reorders_match_golden(oracle_mod, name):
+    m, g = cases.load_golden(name)
+    for kind in ("first_col_sort", "jaccard_greedy", "row_rcm"):
+        if "order_" + kind not in g:
+            continue
+        assert np.array_equal(oracle_mod.reorder_rows(kind, m.M, m.K, m.rowptr, m.colind), g["order_" + kind]), kind
+
+
+@pytest.mark.parametrize("name", sorted(cases.SMALL))
+def test_reorders_match_reference_build(oracle_mod, name):
+    if not oracle_mod.ref_available():
+        pytest.skip("oracle/_ref not built (needs a checkout of the reference project)")
+    m = cases.SMALL[name]()
+    for kind in ("first_col_sort", "jaccard_greedy") + (("row_rcm",) if m.M == m.K else ()):
+        a = oracle_mod.reorder_rows(kind, m.M, m.K, m.rowptr, m.colind)
+        assert np.array_equal(a, oracle_mod.ref_reorder_rows(kind, m.M, m.K, m.rowptr, m.colind)), kind
+        assert sorted(a.tolist()) == list(range(m.M))
