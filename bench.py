@@ -411,7 +411,7 @@ def main():
     roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
                 "traffic": NCU_TRAFFIC_BYTES.get((args.workload, args.scale, N, args.format)) if world == 1 else None,
                 "peak_source": peak_src, "bytes_algorithmic": bytes_alg,
-                "kernel_ms": kernel_ms, "kernel": ("spmm_umma_kernel" if (args.umma and N % 512 == 0 and args.format == "srbcrs") else "spmm_async_kernel") + " (+ spmm_fixup_kernel)",
+                "kernel_ms": kernel_ms, "kernel": ("spmm_umma_kernel" if (args.umma and (N % 512 == 0 or (args.format == "metcf" and N % 128 == 0))) else "spmm_async_kernel") + " (+ spmm_fixup_kernel)",
                 "bytes_gather_no_reuse": bytes_alg - 4 * N * distinct + 4 * N * G_rows,
                 "padded_tile_tflop": 256.0 * packed.T * N / 1e12,
                 "tf32_dense_peak_tflops_measured": tf32_tflops,

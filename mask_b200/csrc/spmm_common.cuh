@@ -107,7 +107,7 @@ __device__ __forceinline__ void flush_fragment(const SpmmArgs& p, int ff, int co
     }
 }
 
-// spmm_umma.cu: tcgen05 / tensor-memory variant (SR-BCRS, N % 512 == 0, groups of at most
+// spmm_umma.cu: tcgen05 / tensor-memory variant (SR-BCRS, N % 128 == 0, groups of at most
 // kUmmaMaxGroupTiles tiles).
 constexpr int kUmmaMaxGroupTiles = 256;
 int launch_spmm_umma(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st);

@@ -41,7 +41,7 @@ static int g_tune_min_blocks = 0;
 static int g_tune_async = 1;   // 1 = shared-memory ring fed by cp.async (SR-BCRS), 0 = register pipeline
 static int g_tune_stages = 0;
 static int g_tune_hints = 0;
-static int g_tune_umma = 1;    // 1 = tcgen05 kernel where it applies (SR-BCRS, N % 512 == 0, groups <= 256 tiles)
+static int g_tune_umma = 1;    // 1 = tcgen05 kernel where it applies (see launch_spmm), 2 = whenever N % 128 == 0
 
 template <int NQ, bool METCF, int MIN_BLOCKS>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, MIN_BLOCKS) spmm_mma_kernel(const SpmmArgs p) {
@@ -281,7 +281,11 @@ static int launch_spmm(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
     // four warps of them, else narrower slabs so that small N still spreads over a block
     const int N = a.N;
     a.hints = g_tune_hints;
-    if (!METCF && g_tune_umma != 0 && N % 512 == 0 && plan->max_group_tiles <= kUmmaMaxGroupTiles) {
+    // tcgen05 kernel: wins when a block covers 512 columns (4 slabs share one tile fetch and one
+    // pipeline step); with 1-2 slabs the mma.sync ring kernel is 10-30 % faster for SR-BCRS, while
+    // for ME-TCF it beats the register-pipelined kernel at every width.  umma = 2 forces it.
+    const bool umma_fits = N % 128 == 0 && plan->max_group_tiles <= kUmmaMaxGroupTiles;
+    if (umma_fits && (g_tune_umma == 2 || (g_tune_umma == 1 && (METCF || N % 512 == 0)))) {
         int rc = launch_spmm_umma(plan, a, st);
         if (rc != MASK_OK) return rc;
         return launch_fixup(plan, a, st);

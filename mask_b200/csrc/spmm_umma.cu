@@ -45,20 +45,22 @@
 namespace mask {
 
 constexpr int kUmmaThreads = 352;
-constexpr int kUmmaStages = 6;
-constexpr int kUmmaSlabs = 4;                       // 4 x 128 = 512 columns per block
-constexpr int kUmmaBBytes = kUmmaSlabs * 4096;      // gathered rows of one tile
 constexpr int kUmmaABytes = 512;
 constexpr int kUmmaIdsBytes = kUmmaMaxGroupTiles * kTileCols * 4;
-constexpr int kUmmaTmemCols = 128;
 constexpr long long kUmmaWaitCycles = 2000000000LL;
 
+// NSLAB 128-column slabs per block (N % (128*NSLAB) == 0), S ring stages.
+template <int NSLAB, int S>
 struct UmmaLayout {
+    static constexpr int kBBytes = NSLAB * 4096;                  // gathered rows of one tile
+    static constexpr int kTmemCols = 32 * NSLAB;                  // two accumulator buffers of 16*NSLAB columns
     static constexpr int kB = 0;
-    static constexpr int kA = kUmmaStages * kUmmaBBytes;
-    static constexpr int kIds = kA + kUmmaStages * kUmmaABytes;
-    static constexpr int kBars = kIds + kUmmaIdsBytes;            // full[S], empty[S], ready[S], acc_full[2], acc_empty[2]
-    static constexpr int kTmemSlot = kBars + (3 * kUmmaStages + 4) * 8;
+    static constexpr int kA = S * kBBytes;
+    static constexpr int kIds = kA + S * kUmmaABytes;
+    static constexpr int kRuns = kIds + kUmmaIdsBytes;            // ME-TCF: [begin, end) of every tile's COO run
+    static constexpr int kCoo = kRuns + kUmmaMaxGroupTiles * 8;   // ME-TCF: per stage 32 idx + 32 val of the run
+    static constexpr int kBars = kCoo + S * 256;                  // full[S], empty[S], ready[S], acc_full[2], acc_empty[2]
+    static constexpr int kTmemSlot = kBars + (3 * S + 4) * 8;
     static constexpr int kAbort = kTmemSlot + 8;
     static constexpr int kBytes = kAbort + 8;
     static constexpr int kDynamicBytes = kBytes + 1024;           // room to align the base to 1024 B
@@ -128,12 +130,21 @@ __device__ __forceinline__ void cp16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 
-__global__ void __launch_bounds__(kUmmaThreads, 2) spmm_umma_kernel(const SpmmArgs p, int32_t* status) {
+// METCF: the tile operand is rebuilt per tile from its COO run (examples/src_fp32/dtc/testbed/
+// kernel.inc:822-840 does the same in its shared-memory restore step).  ME-TCF's index
+// Swizzle<1,2,3>(8r+c) is exactly the K-major SWIZZLE_32B operand layout, so tile[idx] = value
+// yields the operand directly, rows unpermuted.
+template <int NSLAB, int S, int MIN_BLOCKS, bool METCF>
+__global__ void __launch_bounds__(kUmmaThreads, MIN_BLOCKS) spmm_umma_kernel(const SpmmArgs p, int32_t* status) {
+    constexpr int kUmmaStages = S;
+    constexpr int kUmmaSlabs = NSLAB;
+    constexpr int kUmmaBBytes = NSLAB * 4096;
+    constexpr int kAccCols = 16 * NSLAB;                          // accumulator columns per buffer
     extern __shared__ unsigned char umma_smem_raw[];
     const uint32_t raw = (uint32_t)__cvta_generic_to_shared(umma_smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;            // swizzle patterns are functions of the address bits
     unsigned char* gbase = umma_smem_raw + (base - raw);
-    using L = UmmaLayout;
+    using L = UmmaLayout<NSLAB, S>;
     const uint32_t bars = base + L::kBars;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (kUmmaStages + s); };
@@ -164,7 +175,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) spmm_umma_kernel(const SpmmAr
     }
     if (warp == 4) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(base + L::kTmemSlot),
-                     "r"(kUmmaTmemCols)
+                     "r"(L::kTmemCols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -172,6 +183,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) spmm_umma_kernel(const SpmmAr
         const int pt = tid - 224;
         const int chunks = n_tiles * 2;
         for (int c = pt; c < chunks; c += 128) cp16(base + L::kIds + c * 16, p.val_sidx + (int64_t)t0 * kTileCols + c * 4);
+        if (METCF) {  // run offsets: coo_off[2t], coo_off[2t+1]; 2*t0 ints in is 8-byte aligned only, so copy by 8 bytes
+            for (int c = pt; c < n_tiles; c += 128)
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(base + L::kRuns + c * 8), "l"(p.coo_off + 2 * (int64_t)(t0 + c)) : "memory");
+        }
         asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -181,11 +196,11 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) spmm_umma_kernel(const SpmmAr
 
     if (warp >= 7) {
         // ------------------------------ producers ------------------------------------------------
-        const int pw = warp - 7;                 // slab of this warp
+        const int pw = warp - 7;                 // this warp copies 32-column atom pw of every slab
         const int lr = lane >> 3, lc = lane & 7; // row (and row + 4), 16-byte chunk
-        const uint32_t off0 = (uint32_t)(lr * 128 + ((lc ^ (2 * lr)) * 16));   // 32-byte chunks swizzled by row % 4
-        const uint32_t off1 = off0 + 512;                                     // row + 4: same swizzle phase
-        const char* Bcol = reinterpret_cast<const char*>(p.B + col0 + 128 * pw + 4 * lc);
+        const uint32_t off0 = (uint32_t)(pw * 1024 + lr * 128 + ((lc ^ (2 * lr)) * 16));   // 32-byte chunks swizzled by row % 4
+        const uint32_t off1 = off0 + 512;                                                 // row + 4: same swizzle phase
+        const char* Bcol = reinterpret_cast<const char*>(p.B + col0 + 32 * pw + 4 * lc);
         const uint32_t ldb_bytes = (uint32_t)(p.ldb * 4);
         const int* ids = reinterpret_cast<const int*>(gbase + L::kIds);
         int s = 0;
@@ -194,13 +209,26 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) spmm_umma_kernel(const SpmmAr
             if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag)) break;
             const char* r0 = Bcol + (uint64_t)(uint32_t)ids[rel * kTileCols + lr] * ldb_bytes;
             const char* r1 = Bcol + (uint64_t)(uint32_t)ids[rel * kTileCols + lr + 4] * ldb_bytes;
-            const uint32_t dst = base + L::kB + s * kUmmaBBytes + pw * 4096;
+            const uint32_t dst = base + L::kB + s * kUmmaBBytes;
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                cp16(dst + j * 1024 + off0, r0 + j * 128);
-                cp16(dst + j * 1024 + off1, r1 + j * 128);
+            for (int i = 0; i < kUmmaSlabs; i++) {
+                cp16(dst + i * 4096 + off0, r0 + i * 512);
+                cp16(dst + i * 4096 + off1, r1 + i * 512);
             }
-            if (pw == 0) cp16(base + L::kA + s * kUmmaABytes + lane * 16, p.val_blk + (int64_t)(t0 + rel) * kTileElems + lane * 4);
+            if (pw == 0) {
+                if (METCF) {
+                    // first 32 entries of the run (runs start on multiples of 8 entries and are padded to 8)
+                    const int2 run = reinterpret_cast<const int2*>(gbase + L::kRuns)[rel];
+                    const int chunk = lane & 7;   // 4 entries
+                    if (lane < 16 && run.x + 4 * chunk < ((run.y + 7) & ~7)) {
+                        const void* src = lane < 8 ? static_cast<const void*>(p.coo_idx + run.x + 4 * chunk)
+                                                   : static_cast<const void*>(p.coo_val + run.x + 4 * chunk);
+                        cp16(base + L::kCoo + s * 256 + lane * 16, src);
+                    }
+                } else {
+                    cp16(base + L::kA + s * kUmmaABytes + lane * 16, p.val_blk + (int64_t)(t0 + rel) * kTileElems + lane * 4);
+                }
+            }
             // arrives on full[s] once every copy this thread has issued so far has landed
             asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(full_bar(s)) : "memory");
             if (++s == kUmmaStages) { s = 0; round++; }
@@ -213,7 +241,19 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) spmm_umma_kernel(const SpmmAr
             const int s = rel % kUmmaStages;
             const uint32_t round = (uint32_t)(rel / kUmmaStages);
             if (!mbar_wait(full_bar(s), round & 1, abort_flag)) break;
-            if (!(p.hints & 4)) {  // round the tile values to TF32 (nearest, ties away) in place
+            if (METCF) {  // rebuild the 16x8 operand: zero, then tile[idx] = rna(value) over the run
+                uint32_t* tile = reinterpret_cast<uint32_t*>(gbase + L::kA + s * kUmmaABytes);
+                reinterpret_cast<uint4*>(tile)[lane] = make_uint4(0u, 0u, 0u, 0u);
+                __syncwarp();
+                const int2 run = reinterpret_cast<const int2*>(gbase + L::kRuns)[rel];
+                const int cnt = run.y - run.x;
+                const int* sidx = reinterpret_cast<const int*>(gbase + L::kCoo + s * 256);
+                const uint32_t* sval = reinterpret_cast<const uint32_t*>(gbase + L::kCoo + s * 256 + 128);
+                if (lane < cnt) tile[sidx[lane]] = sval[lane] + 0x1000u;
+                for (int e = run.x + 32 + lane; e < run.y; e += 32)   // dense tiles: entries beyond the staged 32
+                    tile[__ldg(p.coo_idx + e)] = __float_as_uint(__ldg(p.coo_val + e)) + 0x1000u;
+                __syncwarp();
+            } else if (!(p.hints & 4)) {  // round the tile values to TF32 (nearest, ties away) in place
                 uint4* at = reinterpret_cast<uint4*>(gbase + L::kA + s * kUmmaABytes) + lane;
                 uint4 v = *at;
                 v.x += 0x1000u; v.y += 0x1000u; v.z += 0x1000u; v.w += 0x1000u;
@@ -243,7 +283,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) spmm_umma_kernel(const SpmmAr
 #pragma unroll
                     for (int slab = 0; slab < kUmmaSlabs; slab++) {
                         const uint64_t adesc = umma_smem_desc(base + L::kB + s * kUmmaBBytes + slab * 4096, 64, 32, kSwizzle128B32B);
-                        umma_tf32(tmem_base + buf * 64 + slab * 16, adesc, bdesc, i > 0 ? 1u : 0u);
+                        umma_tf32(tmem_base + buf * kAccCols + slab * 16, adesc, bdesc, i > 0 ? 1u : 0u);
                     }
                     umma_commit(empty_bar(s));   // the slot is free once these MMAs have read it
                     if (++s == kUmmaStages) { s = 0; round++; }
@@ -279,7 +319,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) spmm_umma_kernel(const SpmmAr
             } else {
                 if (!mbar_wait(accf_bar(buf), uses[buf] & 1, abort_flag)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t taddr = tmem_base + ((uint32_t)(32 * warp) << 16) + buf * 64;
+                const uint32_t taddr = tmem_base + ((uint32_t)(32 * warp) << 16) + buf * kAccCols;
 #pragma unroll
                 for (int sl = 0; sl < kUmmaSlabs; sl++) tmem_ld16(taddr + sl * 16, v[sl]);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -291,7 +331,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) spmm_umma_kernel(const SpmmAr
             }
 #pragma unroll
             for (int i = 0; i < 16; i++) {
-                const int r = i ^ (i >> 3);   // MMA-N index -> window row (rows 8..15 swapped pairwise)
+                const int r = METCF ? i : (i ^ (i >> 3));   // MMA-N index -> window row (SR-BCRS: rows 8..15 swapped pairwise)
                 if (r < rows_ok) {
                     float* row = (slot < 0 && p.row_map) ? p.C + (int64_t)p.row_map[w * kWinRows + r] * p.ldc : dst + (int64_t)r * ld;
 #pragma unroll
@@ -310,20 +350,30 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) spmm_umma_kernel(const SpmmAr
     __syncthreads();
     if (warp == 4) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kUmmaTmemCols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::kTmemCols) : "memory");
     }
     if (tid == 0 && *abort_flag) atomicExch(status, 1);
 }
 
-int launch_spmm_umma(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st) {
-    if (a.N % (kUmmaSlabs * 128) != 0) return fail(MASK_ERR_INVALID_ARGUMENT, "the tcgen05 kernel needs N % 512 == 0");
-    if (plan->max_group_tiles > kUmmaMaxGroupTiles) return fail(MASK_ERR_INVALID_ARGUMENT, "plan groups too large for the tcgen05 kernel");
-    MASK_CUDA_TRY(cudaFuncSetAttribute(spmm_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, UmmaLayout::kDynamicBytes));
-    dim3 grid((unsigned)plan->G, (unsigned)(a.N / (kUmmaSlabs * 128)));
+template <int NSLAB, int S, int MIN_BLOCKS>
+static int launch_umma_variant(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st) {
+    using L = UmmaLayout<NSLAB, S>;
+    auto kern = a.coo_off ? spmm_umma_kernel<NSLAB, S, MIN_BLOCKS, true> : spmm_umma_kernel<NSLAB, S, MIN_BLOCKS, false>;
+    MASK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));
+    dim3 grid((unsigned)plan->G, (unsigned)(a.N / (NSLAB * 128)));
     if (grid.y > 65535) return fail(MASK_ERR_INVALID_ARGUMENT, "N too large");
-    spmm_umma_kernel<<<grid, kUmmaThreads, UmmaLayout::kDynamicBytes, st>>>(a, plan->d_status);
+    kern<<<grid, kUmmaThreads, L::kDynamicBytes, st>>>(a, plan->d_status);
     MASK_CUDA_TRY(cudaGetLastError());
     return MASK_OK;
+}
+
+int launch_spmm_umma(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st) {
+    if (a.N % 128 != 0) return fail(MASK_ERR_INVALID_ARGUMENT, "the tcgen05 kernel needs N % 128 == 0");
+    if (plan->max_group_tiles > kUmmaMaxGroupTiles) return fail(MASK_ERR_INVALID_ARGUMENT, "plan groups too large for the tcgen05 kernel");
+    // widest slab group that divides N: the tile values and ids are fetched once per block
+    if (a.N % 512 == 0) return launch_umma_variant<4, 6, 2>(plan, a, st);
+    if (a.N % 256 == 0) return launch_umma_variant<2, 8, 2>(plan, a, st);
+    return launch_umma_variant<1, 8, 3>(plan, a, st);
 }
 
 }  // namespace mask

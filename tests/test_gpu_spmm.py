@@ -110,8 +110,9 @@ def test_srbcrs_spmm_kernel_variants(oracle_mod, name, N, use_async, nq, knob):
     _assert_close(oracle_mod, m, B, out.cpu().numpy())
 
 
-@pytest.mark.parametrize("name", ["m1", "m17", "m33_empty_window", "hub_rows", "rmat10", "stencil8", "all_empty"])
-@pytest.mark.parametrize("N", [32, 512])
+@pytest.mark.parametrize("name", ["m1", "m17", "m33_empty_window", "hub_rows", "rmat10", "stencil8", "all_empty",
+                                  "one_tile_windows"])
+@pytest.mark.parametrize("N", [32, 128, 256, 512])
 def test_metcf_spmm_matches_oracle(oracle_mod, name, N):
     import torch
     from mask_b200 import engine
@@ -123,8 +124,16 @@ def test_metcf_spmm_matches_oracle(oracle_mod, name, N):
     engine.spmm(p, torch.from_numpy(B).cuda(), out=out, policy="auto")
     _assert_close(oracle_mod, m, B, out.cpu().numpy())
     # a dense tile with more than 32 entries exercises the long-run path
-    out2 = engine.spmm(p, torch.from_numpy(B).cuda(), plan=engine.Plan(p.val_soff, m.M, p.T, "auto", 2))
+    plan2 = engine.Plan(p.val_soff, m.M, p.T, "auto", 2)
+    out2 = engine.spmm(p, torch.from_numpy(B).cuda(), plan=plan2)
     _assert_close(oracle_mod, m, B, out2.cpu().numpy())
+    assert plan2.status() == 0
+    try:  # and the mma.sync ME-TCF kernel
+        engine.tune("umma", 0)
+        out3 = engine.spmm(p, torch.from_numpy(B).cuda(), plan=plan2)
+    finally:
+        engine.tune("umma", 1)
+    _assert_close(oracle_mod, m, B, out3.cpu().numpy())
 
 
 def test_relu_epilogue(oracle_mod):
@@ -221,9 +230,11 @@ def test_medium_rmat_against_oracle(oracle_mod):
 
 @pytest.mark.parametrize("name,N,gt", [("m1", 512, 0), ("m17", 512, 0), ("m33_empty_window", 512, 0), ("all_empty", 512, 0),
                                        ("hub_rows", 512, 3), ("hub_rows", 1024, 0), ("rmat12u", 512, 0),
-                                       ("rmat12u", 512, 200), ("stencil8", 1024, 0), ("three_four_tiles", 512, 1)])
+                                       ("rmat12u", 512, 200), ("stencil8", 1024, 0), ("three_four_tiles", 512, 1),
+                                       ("rmat12u", 128, 0), ("hub_rows", 256, 3), ("rmat10", 384, 0), ("m17", 768, 0),
+                                       ("m33_empty_window", 128, 0), ("stencil8", 256, 0)])
 def test_srbcrs_spmm_tcgen05_kernel(oracle_mod, name, N, gt):
-    """The tcgen05 / tensor-memory kernel (N a multiple of 512): same contract, its bounded waits
+    """The tcgen05 / tensor-memory kernel (N a multiple of 128; 1, 2 or 4 slabs per block): same contract, its bounded waits
     must not have expired, and results are deterministic.  Operand B is truncated to TF32 by the
     tensor core (the tile values are rounded), which stays inside the product tolerance."""
     import torch
@@ -235,7 +246,7 @@ def test_srbcrs_spmm_tcgen05_kernel(oracle_mod, name, N, gt):
     Bd = torch.from_numpy(B).cuda()
     plan = engine.Plan(p.val_soff, m.M, p.T, "auto", gt)
     try:
-        engine.tune("umma", 1)
+        engine.tune("umma", 2)
         out = torch.full((m.M, N), float("nan"), device="cuda")
         engine.spmm(p, Bd, out=out, plan=plan)
         out2 = torch.full((m.M, N), float("nan"), device="cuda")
