@@ -260,6 +260,8 @@ def main():
     ap.add_argument("--stages", type=int, default=0, help="kernel variant: ring slots per warp (0 = default)")
     ap.add_argument("--no-async", action="store_true", help="use the register-pipelined kernel")
     ap.add_argument("--gcn", action="store_true", help="time the row-sharded 2-layer GCN forward instead (extra line)")
+    ap.add_argument("--baselines", action="store_true",
+                    help="also time cuSPARSE (torch.sparse CSR) and the reference's own SR-BCRS kernel recompiled for sm_100a")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / verification leg")
     ap.add_argument("--no-tf32-probe", action="store_true", help="skip the dense TF32 GEMM peak measurement")
     args = ap.parse_args()
@@ -292,8 +294,18 @@ def main():
     bounds = panel_bounds(m, world, dev)
     r0, r1 = bounds[rank], bounds[rank + 1]
     panel = m.row_slice(r0, r1) if world > 1 else m
-    Bh = G.dense_normal(m.K, N, bseed)
-    Bd = torch.from_numpy(Bh).to(dev)
+    # the dense operand: host-generated (NumPy, seeded) when a host copy is needed anyway (end-to-end
+    # leg, CPU verification); for multi-rank or very large runs it is drawn on the device instead,
+    # so that 8 ranks do not each hold a multi-GiB host copy
+    need_host_B = world == 1 and (not args.no_cpu or args.e2e_steps > 0 or args.baselines)
+    if need_host_B or int(m.K) * N * 4 <= (1 << 31):
+        Bh = G.dense_normal(m.K, N, bseed)
+        Bd = torch.from_numpy(Bh).to(dev)
+    else:
+        Bh = None
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(bseed)
+        Bd = torch.randn((m.K, N), dtype=torch.float32, device=dev, generator=gen)
     rp, ci, va = (torch.from_numpy(np.ascontiguousarray(x)).to(dev) for x in (panel.rowptr, panel.colind, panel.values))
 
     torch.cuda.synchronize()
@@ -342,7 +354,7 @@ def main():
     e2e = None
     host_result = None
     try:
-        if args.e2e_steps <= 0:
+        if args.e2e_steps <= 0 or Bh is None:
             raise RuntimeError("skipped (--e2e-steps 0)")
         hB = torch.from_numpy(Bh).pin_memory()
         hC = torch.empty((panel.M, N), dtype=torch.float32).pin_memory()
@@ -450,6 +462,41 @@ def main():
         if bad:
             log(f"[bench] VERIFICATION FAILED: {bad} elements outside tolerance")
 
+    # ---- same-box GPU baselines (rank 0, single GPU, on request) ----
+    gpu_baselines = None
+    if args.baselines and world == 1 and args.format == "srbcrs":
+        gpu_baselines = {}
+        try:
+            A_t = torch.sparse_csr_tensor(rp.to(torch.int64), ci.to(torch.int64), va, size=(m.M, m.K))
+            for _ in range(3):
+                ref_out = torch.sparse.mm(A_t, Bd)
+            torch.cuda.synchronize()
+            c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            c0.record()
+            for _ in range(10):
+                ref_out = torch.sparse.mm(A_t, Bd)
+            c1.record()
+            torch.cuda.synchronize()
+            cms = c0.elapsed_time(c1) / 10
+            gpu_baselines["cusparse_csr_fp32"] = {"ms": cms, "gflops": 2.0 * m.nnz * N / (cms * 1e-3) / 1e9,
+                                                  "how": "torch.sparse.mm (CSR, FP32) on the same inputs"}
+            del A_t, ref_out
+        except Exception as e:
+            gpu_baselines["cusparse_csr_fp32"] = {"error": str(e)[:200]}
+        try:
+            import oracle
+            if not oracle.ref_gpu_available():
+                raise RuntimeError("oracle/_ref/libref_gpu_srbcrs.so not built")
+            host_packed = {k: getattr(packed, k).cpu().numpy() for k in ("val_soff", "val_sidx", "val_block_val")}
+            host_packed["T"] = packed.T
+            rC, rms = oracle.ref_gpu_srbcrs(m.M, N, m.K, host_packed, Bh, warmup=3, repeat=10)
+            agree = float(np.abs(rC[:4096] - out[:4096].cpu().numpy()).max())
+            gpu_baselines["reference_srbcrs_16x8_kernel_sm100a"] = {
+                "ms": rms, "gflops": 2.0 * m.nnz * N / (rms * 1e-3) / 1e9, "max_abs_diff_first_4096_rows": agree,
+                "how": "sr_bcrs_spmm_kernel_tf32 of the reference (kernel.inc) recompiled for sm_100a, its own grid mapping"}
+        except Exception as e:
+            gpu_baselines["reference_srbcrs_16x8_kernel_sm100a"] = {"error": str(e)[:200]}
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -461,7 +508,7 @@ def main():
                        "partition": "tile-balanced row panels on window boundaries, B replicated" if world > 1 else "none",
                        "l2": "no flush needed: B and C (M*N*4 bytes each) are far larger than the 126 MB L2"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
-            "clocks": clocks.summary(), "verified": verified, "kernel_status": kernel_status,
+            "clocks": clocks.summary(), "verified": verified, "kernel_status": kernel_status, "gpu_baselines": gpu_baselines,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -344,3 +344,24 @@ def ref_multi_bind_plan(M, val_soff):
     R.ref_multi_bind_fetch.argtypes = [_i32p, _i32p, _i32p]
     R.ref_multi_bind_fetch(tw, ws, ts)
     return tw[:P], ws[:W], ts
+
+
+def ref_gpu_available() -> bool:
+    return os.path.exists(os.path.join(_HERE, "_ref", "libref_gpu_srbcrs.so"))
+
+
+def ref_gpu_srbcrs(M, N, K, packed, B, warmup=3, repeat=10):
+    """Runs the reference project's own SR-BCRS 16x8 kernel (recompiled for sm_100a) on host
+    arrays; returns (C, mean kernel ms)."""
+    R = _ref("libref_gpu_srbcrs.so")
+    R.ref_gpu_srbcrs_run.restype = C.c_float
+    R.ref_gpu_srbcrs_run.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _i32p, _i32p, _f32p, _f32p, _f32p, C.c_int,
+                                     C.c_int]
+    B = _c(B, np.float32)
+    out = np.zeros((M, N), dtype=np.float32)
+    ms = float(R.ref_gpu_srbcrs_run(M, N, K, int(packed["T"]), _c(packed["val_sidx"], np.int32),
+                                    _c(packed["val_soff"], np.int32), B, _c(packed["val_block_val"], np.float32), out,
+                                    warmup, repeat))
+    if ms < 0:
+        raise RuntimeError(f"reference GPU kernel failed (code {ms})")
+    return out, ms
