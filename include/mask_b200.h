@@ -133,6 +133,42 @@ int mask_plan_multi_bind(const int32_t* h_val_soff, int32_t M, int32_t* task_win
                          int32_t* window_split, int32_t* task_soff, int64_t* n_tasks);
 
 /* ------------------------------------------------------------------------------------------
+ * Matrix features the execution plan is chosen from (the reference derives a larger set in
+ * examples/src_fp32/dtc/testbed/featurize_mtx.cu:298-401; these are the ones that drive a
+ * decision here).  Percentiles use the bridge's rank rule, heavy_tail is its test
+ * tiles_max > max(64, 4 * p95) (examples/src_fp32/acc/testbed/custom_format_e2e.cu:652-663).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct mask_features {
+    int32_t row_windows;
+    int32_t empty_windows;
+    int64_t tiles;
+    int64_t nnz;
+    double tiles_mean;
+    int32_t tiles_p50, tiles_p95, tiles_p99, tiles_max;
+    double top5_window_share; /* share of all tiles held by the 5 largest windows */
+    double tile_fill;         /* nnz / (128 * tiles) */
+    int32_t heavy_tail;
+} mask_features;
+
+int mask_features_from_soff(const int32_t* h_val_soff, int32_t M, int64_t nnz, mask_features* out);
+
+/* ------------------------------------------------------------------------------------------
+ * ME-TCF packed-format cache file, byte-compatible with the reference's storeCheckpoint /
+ * loadCheckpoint (examples/src_fp32/dtc/testbed/main.cu:217-340): raw little-endian
+ * [T][nnz_pad][val_soff][val_sidx][val_coo_off][val_coo_idx][val_coo_val]; host arrays.
+ * ------------------------------------------------------------------------------------------ */
+int mask_metcf_checkpoint_name(const char* matrix_name, int32_t M, int32_t K, char* out, size_t out_len);
+int mask_metcf_checkpoint_write(const char* path, int32_t M, int64_t T, int64_t nnz_pad,
+                                const int32_t* val_soff, const int32_t* val_sidx,
+                                const int32_t* val_coo_off, const int32_t* val_coo_idx,
+                                const float* val_coo_val);
+int mask_metcf_checkpoint_header(const char* path, int64_t* T, int64_t* nnz_pad);
+/* Arrays sized from the header; validates sizes, offsets and column range like the reference. */
+int mask_metcf_checkpoint_read(const char* path, int32_t M, int32_t K, int64_t T, int64_t nnz_pad,
+                               int32_t* val_soff, int32_t* val_sidx, int32_t* val_coo_off,
+                               int32_t* val_coo_idx, float* val_coo_val);
+
+/* ------------------------------------------------------------------------------------------
  * Execution plan: how tiles are dealt to thread blocks.  Replaces the grid mapping of the
  * reference kernels (one block per window, examples/src_fp32/sr_bcrs/testbed/host_program_16x8.cu:
  * 157-159; strict_lb / multi_bind tables, host_program_strict_lb.cu:163-289).
@@ -143,7 +179,9 @@ typedef enum mask_policy {
     MASK_POLICY_AUTO = 0,      /* window-aligned groups; windows larger than a group are split */
     MASK_POLICY_ROW = 1,       /* one task per window, never split */
     MASK_POLICY_STRICT_LB = 2, /* the reference's strict_lb tables (exact `group_tiles` per block) */
-    MASK_POLICY_MULTI_BIND = 3 /* the reference's multi_bind tables */
+    MASK_POLICY_MULTI_BIND = 3, /* the reference's multi_bind tables */
+    MASK_POLICY_REF_AUTO = 4    /* the bridge's rule: strict_lb if the tile distribution is heavy-tailed,
+                                   else row (custom_format_e2e.cu:659-707) */
 } mask_policy;
 
 /* Builds a plan from val_soff (device).  group_tiles <= 0 picks a default from T and the SM

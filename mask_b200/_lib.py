@@ -26,6 +26,11 @@ SIGNATURES = {
     "mask_reorder_rows": (C.c_int, [C.c_int, vp, vp, i32, i32, vp]),
     "mask_csr_permute_rows": (C.c_int, [vp, vp, vp, i32, vp, vp, vp, vp, vp]),
     "mask_plan_set_row_map": (C.c_int, [vp, vp]),
+    "mask_features_from_soff": (C.c_int, [vp, i32, i64, vp]),
+    "mask_metcf_checkpoint_name": (C.c_int, [C.c_char_p, i32, i32, C.c_char_p, sz]),
+    "mask_metcf_checkpoint_write": (C.c_int, [C.c_char_p, i32, i64, i64, vp, vp, vp, vp, vp]),
+    "mask_metcf_checkpoint_header": (C.c_int, [C.c_char_p, C.POINTER(i64), C.POINTER(i64)]),
+    "mask_metcf_checkpoint_read": (C.c_int, [C.c_char_p, i32, i32, i64, i64, vp, vp, vp, vp, vp]),
     "mask_plan_strict_lb": (C.c_int, [vp, i32, i32, vp, vp, vp, C.POINTER(i64), C.POINTER(i64)]),
     "mask_plan_multi_bind": (C.c_int, [vp, i32, vp, vp, vp, C.POINTER(i64)]),
     "mask_plan_create": (C.c_int, [vp, i32, i64, C.c_int, i32, vp, C.POINTER(vp)]),
@@ -47,7 +52,14 @@ SIGNATURES = {
 }
 
 REORDER = {"none": 0, "row_rcm": 1, "first_col_sort": 2, "jaccard_greedy": 3}
-POLICY = {"auto": 0, "row": 1, "strict_lb": 2, "multi_bind": 3}
+POLICY = {"auto": 0, "row": 1, "strict_lb": 2, "multi_bind": 3, "ref_auto": 4}
+
+
+class Features(C.Structure):
+    """mask_features"""
+    _fields_ = [("row_windows", i32), ("empty_windows", i32), ("tiles", i64), ("nnz", i64), ("tiles_mean", C.c_double),
+                ("tiles_p50", i32), ("tiles_p95", i32), ("tiles_p99", i32), ("tiles_max", i32),
+                ("top5_window_share", C.c_double), ("tile_fill", C.c_double), ("heavy_tail", i32)]
 EPILOGUE_NONE, EPILOGUE_RELU = 0, 1
 
 _lib = None

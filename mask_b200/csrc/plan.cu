@@ -213,7 +213,7 @@ extern "C" int mask_plan_create(const int32_t* d_val_soff, int32_t M, int64_t T,
     MASK_REQUIRE(out != nullptr, "out is NULL");
     *out = nullptr;
     MASK_REQUIRE(d_val_soff != nullptr && M >= 1 && T >= 0, "bad arguments");
-    MASK_REQUIRE(policy >= MASK_POLICY_AUTO && policy <= MASK_POLICY_MULTI_BIND, "unknown policy");
+    MASK_REQUIRE(policy >= MASK_POLICY_AUTO && policy <= MASK_POLICY_REF_AUTO, "unknown policy");
     if (T >= (int64_t)1 << 31) return fail(MASK_ERR_INDEX_OVERFLOW, "T does not fit int32");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     mask_plan* p = new mask_plan();
@@ -233,6 +233,12 @@ extern "C" int mask_plan_create(const int32_t* d_val_soff, int32_t M, int64_t T,
     if (soff[0] != 0 || (int64_t)soff[p->W] != T) {
         delete p;
         return fail(MASK_ERR_INVALID_ARGUMENT, "val_soff does not start at 0 / end at T");
+    }
+    if (policy == MASK_POLICY_REF_AUTO) {  // the bridge's automatic choice between its own two mappings
+        mask_features f;
+        mask_features_from_soff(soff.data(), M, 0, &f);
+        p->policy = f.heavy_tail ? MASK_POLICY_STRICT_LB : MASK_POLICY_ROW;
+        if (group_tiles <= 0) p->group_tiles = 64;
     }
     build_tables(*p, soff.data());
     int rc = upload(p->h_frag_off, &p->d_frag_off, st);

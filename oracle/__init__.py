@@ -313,6 +313,43 @@ def ref_pack_metcf(M, K, rowptr, colind, values):
                 nnz_pad=pad)
 
 
+def ref_metcf_checkpoint_roundtrip(cache_dir, matrix_name, M, K, rowptr, colind, values):
+    """Packs with the reference, writes its checkpoint into cache_dir with the reference's own
+    storeCheckpoint and returns the file path."""
+    R = _ref("libref_metcf.so")
+    os.environ["SPARSENE_MTX_CACHE_DIR"] = cache_dir
+    os.environ.pop("SPARSENE_DISABLE_MTX_CACHE", None)
+    packed = ref_pack_metcf(M, K, rowptr, colind, values)
+    R.ref_metcf_store_checkpoint.restype = C.c_int
+    R.ref_metcf_store_checkpoint.argtypes = [C.c_char_p, C.c_int, C.c_int]
+    fake_path = f"/data/{matrix_name}.mtx".encode()
+    if R.ref_metcf_store_checkpoint(fake_path, M, K) != 1:
+        raise RuntimeError("reference storeCheckpoint failed")
+    return os.path.join(cache_dir, f"{matrix_name}_M{M}_K{K}_TBK8_RWM16_METCF.checkpoint"), packed
+
+
+def ref_metcf_load_checkpoint(cache_dir, matrix_name, M, K):
+    """Loads <cache_dir>/<name>_..._METCF.checkpoint with the reference's own loadCheckpoint."""
+    R = _ref("libref_metcf.so")
+    os.environ["SPARSENE_MTX_CACHE_DIR"] = cache_dir
+    R.ref_metcf_load_checkpoint.restype = C.c_int
+    R.ref_metcf_load_checkpoint.argtypes = [C.c_char_p, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]
+    T, pad = C.c_int(0), C.c_int(0)
+    if R.ref_metcf_load_checkpoint(f"/data/{matrix_name}.mtx".encode(), M, K, C.byref(T), C.byref(pad)) != 1:
+        raise RuntimeError("reference loadCheckpoint failed")
+    T, pad = int(T.value), int(pad.value)
+    W = (M + 15) // 16
+    soff = np.zeros(W + 1, dtype=np.int32)
+    sidx = np.zeros(8 * T, dtype=np.int32)
+    off = np.zeros(2 * T + 1, dtype=np.int32)
+    idx = np.zeros(pad, dtype=np.int32)
+    val = np.zeros(pad, dtype=np.float32)
+    R.ref_metcf_fetch.restype = None
+    R.ref_metcf_fetch.argtypes = [_i32p, _i32p, _i32p, _i32p, _f32p]
+    R.ref_metcf_fetch(soff, sidx, off, idx, val)
+    return dict(val_soff=soff, val_sidx=sidx, val_coo_off=off, val_coo_idx=idx, val_coo_val=val, T=T, nnz_pad=pad)
+
+
 def ref_strict_lb_plan(M, val_soff, workload=64):
     R = _ref("libref_strict_lb.so")
     val_soff = _c(val_soff, np.int32).copy()

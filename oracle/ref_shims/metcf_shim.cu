@@ -42,7 +42,23 @@ void ref_metcf_fetch(int* val_soff, int* val_sidx, int* val_coo_off, int* val_co
     std::memcpy(val_coo_off, g_meta.val_coo_off.data(), sizeof(int) * g_meta.val_coo_off.size());
     std::memcpy(val_coo_idx, g_meta.val_coo_idx.data(), sizeof(int) * g_meta.val_coo_idx.size());
     std::memcpy(val_coo_val, g_meta.val_coo_val.data(), sizeof(float) * g_meta.val_coo_val.size());
+}
+
+// Writes the checkpoint of the last ref_metcf_pack result with the reference's own storeCheckpoint
+// (main.cu:232-285) into the directory named by SPARSENE_MTX_CACHE_DIR; returns its 0/1.
+int ref_metcf_store_checkpoint(const char* matrix_file_path, int M, int K) {
+    return storeCheckpoint(std::string(matrix_file_path), M, K, 0.0f, g_meta.val_sidx, g_meta.val_soff, g_meta.val_coo_idx,
+                           g_meta.val_coo_val, g_meta.val_coo_off, g_meta.total_TCBlock_num, g_meta.nnz_pad);
+}
+
+// Loads a checkpoint with the reference's own loadCheckpoint (main.cu:287-340) into the capture slot.
+int ref_metcf_load_checkpoint(const char* matrix_file_path, int M, int K, int* T, int* nnz_pad) {
     g_meta = METCFMetadata();
+    const int ok = loadCheckpoint(std::string(matrix_file_path), M, K, 0.0f, g_meta.val_sidx, g_meta.val_soff, g_meta.val_coo_idx,
+                                  g_meta.val_coo_val, g_meta.val_coo_off, g_meta.total_TCBlock_num, g_meta.nnz_pad);
+    *T = g_meta.total_TCBlock_num;
+    *nnz_pad = g_meta.nnz_pad;
+    return ok;
 }
 
 }  // extern "C"

@@ -125,3 +125,81 @@ def test_host_reorders_match_golden_and_oracle(oracle_mod, name):
     assert L.mask_reorder_rows(0, m.rowptr.ctypes.data, m.colind.ctypes.data, m.M, m.K, ident.ctypes.data) == 0
     assert np.array_equal(ident, np.arange(m.M))
     assert L.mask_reorder_rows(9, m.rowptr.ctypes.data, m.colind.ctypes.data, m.M, m.K, ident.ctypes.data) == 1
+
+
+def _write_checkpoint(L, path, M, packed):
+    return L.mask_metcf_checkpoint_write(path.encode(), M, packed["T"], packed["nnz_pad"], packed["val_soff"].ctypes.data,
+                                         packed["val_sidx"].ctypes.data, packed["val_coo_off"].ctypes.data,
+                                         packed["val_coo_idx"].ctypes.data, packed["val_coo_val"].ctypes.data)
+
+
+def _read_checkpoint(L, path, M, K):
+    T, pad = C.c_int64(), C.c_int64()
+    assert L.mask_metcf_checkpoint_header(path.encode(), C.byref(T), C.byref(pad)) == 0
+    T, pad = T.value, pad.value
+    W = (M + 15) // 16
+    out = dict(val_soff=np.zeros(W + 1, np.int32), val_sidx=np.zeros(8 * T, np.int32), val_coo_off=np.zeros(2 * T + 1, np.int32),
+               val_coo_idx=np.zeros(pad, np.int32), val_coo_val=np.zeros(pad, np.float32), T=T, nnz_pad=pad)
+    rc = L.mask_metcf_checkpoint_read(path.encode(), M, K, T, pad, out["val_soff"].ctypes.data, out["val_sidx"].ctypes.data,
+                                      out["val_coo_off"].ctypes.data, out["val_coo_idx"].ctypes.data,
+                                      out["val_coo_val"].ctypes.data)
+    return rc, out
+
+
+@pytest.mark.parametrize("name", ["rmat10", "m17", "hub_rows"])
+def test_metcf_checkpoint_file(oracle_mod, tmp_path, name):
+    """Write / read round trip, validation on load, and byte compatibility with the reference's own
+    storeCheckpoint / loadCheckpoint when the reference build is present."""
+    L = _lib.lib()
+    m = cases.SMALL[name]()
+    packed = oracle_mod.pack_metcf(m.M, m.rowptr, m.colind, m.values)
+    buf = C.create_string_buffer(256)
+    assert L.mask_metcf_checkpoint_name(name.encode(), m.M, m.K, buf, 256) == 0
+    fname = buf.value.decode()
+    assert fname == f"{name}_M{m.M}_K{m.K}_TBK8_RWM16_METCF.checkpoint"
+    mine = str(tmp_path / "mine" / fname)
+    os.makedirs(os.path.dirname(mine))
+    assert _write_checkpoint(L, mine, m.M, packed) == 0
+    rc, back = _read_checkpoint(L, mine, m.M, m.K)
+    assert rc == 0
+    for k in ("val_soff", "val_sidx", "val_coo_off", "val_coo_idx", "val_coo_val"):
+        assert np.array_equal(back[k].view(np.int32), packed[k].view(np.int32)), k
+    # a column outside [0, K) or a truncated file is refused
+    assert _read_checkpoint(L, mine, m.M, 1)[0] == 6
+    with open(mine, "rb") as f:
+        blob = f.read()
+    short = str(tmp_path / "short.checkpoint")
+    with open(short, "wb") as f:
+        f.write(blob[:-8])
+    T, pad = C.c_int64(), C.c_int64()
+    assert L.mask_metcf_checkpoint_header(short.encode(), C.byref(T), C.byref(pad)) == 0
+    assert _read_checkpoint(L, short, m.M, m.K)[0] == 1
+    if oracle_mod.ref_available():
+        ref_dir = str(tmp_path / "ref")
+        os.makedirs(ref_dir)
+        ref_path, _ = oracle_mod.ref_metcf_checkpoint_roundtrip(ref_dir, name, m.M, m.K, m.rowptr, m.colind, m.values)
+        with open(ref_path, "rb") as f:
+            assert f.read() == blob                     # same bytes as the reference writes
+        loaded = oracle_mod.ref_metcf_load_checkpoint(os.path.dirname(mine), name, m.M, m.K)   # reference reads ours
+        for k in ("val_soff", "val_sidx", "val_coo_off", "val_coo_idx", "val_coo_val"):
+            assert np.array_equal(loaded[k].view(np.int32), packed[k].view(np.int32)), k
+
+
+def test_features_and_ref_auto_rule(oracle_mod):
+    L = _lib.lib()
+    for name in ("rmat12u", "hub_rows", "stencil8", "all_empty", "m1"):
+        m = cases.SMALL[name]()
+        soff = oracle_mod.pack_srbcrs(m.M, m.rowptr, m.colind, m.values)["val_soff"]
+        f = _lib.Features()
+        assert L.mask_features_from_soff(soff.ctypes.data, m.M, m.nnz, C.byref(f)) == 0
+        lens = np.sort(np.diff(soff))
+        W = len(lens)
+        rank = lambda q: int(lens[min(W - 1, int(np.ceil(W * q)) - 1)])
+        assert (f.row_windows, f.tiles, f.nnz) == (W, int(soff[-1]), m.nnz)
+        assert (f.tiles_p50, f.tiles_p95, f.tiles_p99, f.tiles_max) == (rank(0.5), rank(0.95), rank(0.99), int(lens[-1]))
+        assert f.empty_windows == int((lens == 0).sum())
+        assert abs(f.tiles_mean - (soff[-1] / W)) < 1e-12
+        assert f.heavy_tail == int(lens[-1] > max(64, 4 * max(rank(0.95), 1)))
+        if soff[-1]:
+            assert abs(f.tile_fill - m.nnz / (128.0 * soff[-1])) < 1e-12
+            assert abs(f.top5_window_share - lens[-5:].sum() / soff[-1]) < 1e-12

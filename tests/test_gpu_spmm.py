@@ -58,7 +58,7 @@ def test_srbcrs_spmm_column_counts(oracle_mod, N):
 
 
 @pytest.mark.parametrize("policy,gt", [("auto", 0), ("auto", 2), ("row", 0), ("strict_lb", 0), ("strict_lb", 3),
-                                       ("multi_bind", 0)])
+                                       ("multi_bind", 0), ("ref_auto", 0)])
 @pytest.mark.parametrize("name", ["hub_rows", "rmat10", "m33_empty_window", "all_empty", "m17"])
 def test_srbcrs_spmm_policies(oracle_mod, name, policy, gt):
     """Every task mapping (including windows split over several blocks and summed from scratch)
