@@ -124,18 +124,19 @@ def build_workload(name: str, scale: int | None):
 
 
 def panel_bounds(m, parts: int, dev) -> list[int]:
-    """Row panel boundaries on 16-row window boundaries.  Panels are balanced by 16x8 tile count
-    (the kernel's cost unit; equal to balanced nnz up to tile fill): every rank runs the cheap
-    window analysis of the device format builder on the whole matrix to get tiles per window."""
+    """Row panel boundaries on 16-row window boundaries.  Panels are balanced by a cost model of
+    the kernel -- 16x8 tiles plus a fixed share per window for the rows of C it writes (equal to
+    balanced nnz up to tile fill and row count): every rank runs the cheap window analysis of the
+    device format builder on the whole matrix to get tiles per window."""
     if parts == 1:
         return [0, m.M]
     import torch
     from mask_b200 import engine
-    from mask_b200.sharding import balanced_panels
+    from mask_b200.sharding import balanced_panels, spmm_cost_prefix
     rp = torch.from_numpy(m.rowptr).to(dev)
     ci = torch.from_numpy(m.colind).to(dev)
     _, val_soff, _, _ = engine._analyze(rp, ci, m.M, m.K)
-    return balanced_panels(val_soff.cpu().numpy(), m.M, parts)
+    return balanced_panels(spmm_cost_prefix(val_soff.cpu().numpy()), m.M, parts)
 
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the dominant kernel,
@@ -273,6 +274,10 @@ def main():
     import torch.distributed as dist
     from mask_b200 import _lib, engine, generators as G
 
+    # keep stdout to the one JSON line: NCCL's version banner (NCCL_DEBUG=VERSION) goes to stderr
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -344,7 +349,11 @@ def main():
     total_ms = ev[0].elapsed_time(ev[-1])
     per_launch = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
     t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    per_rank_ms = [total_ms / args.steps]
     if world > 1:
+        every = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(every, t)
+        per_rank_ms = [float(x.item()) / args.steps for x in every]
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_per_step = float(t.item()) / args.steps
     value = 2.0 * m.nnz * N / (ms_per_step * 1e-3) / 1e9
@@ -505,7 +514,9 @@ def main():
             "config": {"workload": args.workload + (f" scale={args.scale}" if args.scale else ""), "M": m.M, "K": m.K,
                        "nnz": m.nnz, "N": N, "format": "SR-BCRS 16x8" if args.format == "srbcrs" else "ME-TCF",
                        "tiles_rank0": packed.T, "policy": args.policy, "plan": info, "pack_ms_rank0": pack_ms,
-                       "partition": "tile-balanced row panels on window boundaries, B replicated" if world > 1 else "none",
+                       "partition": "row panels on window boundaries balanced by tiles + 5 per window, B replicated" if world > 1 else "none",
+                       "panel_rows": [bounds[i + 1] - bounds[i] for i in range(world)],
+                       "per_rank_ms": [round(x, 4) for x in per_rank_ms],
                        "l2": "no flush needed: B and C (M*N*4 bytes each) are far larger than the 126 MB L2"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks.summary(), "verified": verified, "kernel_status": kernel_status, "gpu_baselines": gpu_baselines,

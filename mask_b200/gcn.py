@@ -143,3 +143,9 @@ def tile_prefix_on_device(csr, device) -> np.ndarray:
     ci = torch.from_numpy(csr.colind).to(device)
     _, val_soff, _, _ = engine._analyze(rp, ci, csr.M, csr.K)
     return val_soff.cpu().numpy()
+
+
+def cost_prefix_on_device(csr, device) -> np.ndarray:
+    """Per-window cost prefix (tiles plus a fixed share per window) for balancing panels and chunks."""
+    from .sharding import spmm_cost_prefix
+    return spmm_cost_prefix(tile_prefix_on_device(csr, device))

@@ -38,6 +38,19 @@ def balanced_panels(win_prefix: np.ndarray, M: int, parts: int) -> list[int]:
     return bounds
 
 
+# A window costs its tiles plus a fixed part for the 16 rows of C it writes.  Fitted on the
+# 2^20-node power-law graph at N = 512 over 8 GPUs with equal tile counts per rank: per-rank time
+# 0.393 ms (8.7 k rows) ... 0.570 ms (392 k rows) = 1.58e-6 ms per tile + 4.6e-7 ms per row, i.e. one
+# window of 16 rows weighs about as much as 4.7 tiles.
+WINDOW_OVERHEAD_TILES = 5
+
+
+def spmm_cost_prefix(val_soff: np.ndarray, window_overhead_tiles: int = WINDOW_OVERHEAD_TILES) -> np.ndarray:
+    """Exclusive prefix of the per-window SpMM cost model (tiles + a fixed share per window)."""
+    soff = np.asarray(val_soff).astype(np.int64)
+    return soff + window_overhead_tiles * np.arange(soff.shape[0], dtype=np.int64)
+
+
 def nnz_balanced_panels(rowptr: np.ndarray, M: int, parts: int) -> list[int]:
     """Panels holding equal numbers of stored entries."""
     assert rowptr.shape[0] == M + 1

@@ -29,6 +29,8 @@ def test_panels_are_window_aligned_and_balanced():
     b = balanced_panels(prefix, 40, 8)
     assert b[0] == 0 and b[-1] == 40 and all(x <= y for x, y in zip(b, b[1:]))
     assert chunk_bounds(prefix, 40, 16, 40, 2)[0] == 16 and chunk_bounds(prefix, 40, 16, 40, 2)[-1] == 40
+    from mask_b200.sharding import spmm_cost_prefix
+    assert spmm_cost_prefix(prefix, 5).tolist() == [0, 10, 15, 24]
 
 
 def _free_port():
