@@ -200,6 +200,25 @@ int mask_plan_info(const mask_plan* plan, int64_t* n_frag, int64_t* n_groups, in
  * order with no separate pass.  Replaces the bridge's host-side unpack_output
  * (custom_format_e2e.cu:1083-1100).  The array (M entries) is not owned by the plan. */
 int mask_plan_set_row_map(mask_plan* plan, const int32_t* d_row_order);
+/* Fused SpMM + all-gather for row-sharded multi-GPU use: every SpMM launched with this plan also
+ * stores each finished output row into n_peers more buffers (d_peer_ptrs is a device array of
+ * their bases, laid out like d_C; at most 15; NULL / 0 switches it off).  With peer-mapped
+ * buffers of the other GPUs (plain P2P stores over NVLink) each rank's panel of C lands in every
+ * rank's full copy while the product is still running, and no separate collective is needed:
+ * only a barrier after the kernels.  The reference is single-GPU and has no counterpart.  The
+ * pointer array is not owned by the plan. */
+int mask_plan_set_peer_outputs(mask_plan* plan, float* const* d_peer_ptrs, int32_t n_peers);
+/* Buffers for d_peer_ptrs when every GPU has its own process (no counterpart in the reference).
+ * mask_peer_alloc: one cudaMalloc on the current device plus its CUDA IPC handle
+ * (MASK_PEER_HANDLE_BYTES bytes, to be sent to the other processes by the host program's own
+ * channel).  mask_peer_open, in another process of the same machine: maps that buffer for the
+ * current device (peer access is switched on as needed) and returns its address there.  Close
+ * every mapping (mask_peer_close) before the owner frees the buffer (mask_peer_free). */
+#define MASK_PEER_HANDLE_BYTES 64
+int mask_peer_alloc(size_t bytes, void** d_ptr, void* handle);
+int mask_peer_open(const void* handle, void** d_ptr);
+int mask_peer_close(void* d_ptr);
+int mask_peer_free(void* d_ptr);
 /* Reads the plan's device status word (synchronises): 0, or non-zero if a kernel launched with
  * this plan gave up on one of its bounded waits (its output is then invalid).  No counterpart in
  * the reference, whose kernels have no waits. */

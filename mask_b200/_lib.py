@@ -26,6 +26,11 @@ SIGNATURES = {
     "mask_reorder_rows": (C.c_int, [C.c_int, vp, vp, i32, i32, vp]),
     "mask_csr_permute_rows": (C.c_int, [vp, vp, vp, i32, vp, vp, vp, vp, vp]),
     "mask_plan_set_row_map": (C.c_int, [vp, vp]),
+    "mask_plan_set_peer_outputs": (C.c_int, [vp, vp, i32]),
+    "mask_peer_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p), vp]),
+    "mask_peer_open": (C.c_int, [vp, C.POINTER(C.c_void_p)]),
+    "mask_peer_close": (C.c_int, [vp]),
+    "mask_peer_free": (C.c_int, [vp]),
     "mask_features_from_soff": (C.c_int, [vp, i32, i64, vp]),
     "mask_metcf_checkpoint_name": (C.c_int, [C.c_char_p, i32, i32, C.c_char_p, sz]),
     "mask_metcf_checkpoint_write": (C.c_int, [C.c_char_p, i32, i64, i64, vp, vp, vp, vp, vp]),

@@ -290,6 +290,15 @@ extern "C" int mask_plan_set_row_map(mask_plan* p, const int32_t* d_row_order) {
     return MASK_OK;
 }
 
+extern "C" int mask_plan_set_peer_outputs(mask_plan* p, float* const* d_peer_ptrs, int32_t n_peers) {
+    using namespace mask;
+    MASK_REQUIRE(p != nullptr, "plan is NULL");
+    MASK_REQUIRE(n_peers >= 0 && n_peers <= 15 && (n_peers == 0 || d_peer_ptrs != nullptr), "bad peer list");
+    p->d_peer_out = n_peers ? d_peer_ptrs : nullptr;
+    p->n_peer_out = n_peers;
+    return MASK_OK;
+}
+
 extern "C" int mask_plan_status(const mask_plan* p, int32_t* h_status, void* stream) {
     using namespace mask;
     MASK_REQUIRE(p != nullptr && h_status != nullptr, "NULL argument");

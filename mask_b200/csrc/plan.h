@@ -30,5 +30,7 @@ struct mask_plan {
     int32_t* d_group_off = nullptr;
     int32_t* d_head_frag = nullptr;
     const int32_t* d_row_map = nullptr;  // optional, not owned: output row of packed row i (a row reorder's order[])
+    float* const* d_peer_out = nullptr;  // optional, not owned: device array of n_peer_out extra output bases
+    int32_t n_peer_out = 0;
     int32_t* d_status = nullptr;  // device status word: non-zero after a kernel gave up on a bounded wait
 };

@@ -16,6 +16,8 @@ struct SpmmArgs {
     const int32_t* coo_off;    // ME-TCF
     const int32_t* coo_idx;
     const float* coo_val;
+    float* const* peer_out;    // optional: n_peer_out more output bases (peer GPUs' copies of C, same layout)
+    int32_t n_peer_out;
     const int32_t* row_map;    // optional: packed row i is output row row_map[i] (row reorder undone on the fly)
     const float* B;
     int64_t ldb;
@@ -98,6 +100,14 @@ __device__ __forceinline__ void flush_fragment(const SpmmArgs& p, int ff, int co
                     if (c0 < p.N) *reinterpret_cast<float4*>(row + c0) = v0;
                     if (c0 + 4 < p.N) *reinterpret_cast<float4*>(row + c0 + 4) = v1;
                 }
+                if (slot < 0) {  // the same row into every peer's copy of C (plain stores over NVLink)
+                    const int64_t off = row - p.C;
+                    for (int j = 0; j < p.n_peer_out; j++) {
+                        float* prow = p.peer_out[j] + off;
+                        if (c0 < p.N) *reinterpret_cast<float4*>(prow + c0) = v0;
+                        if (c0 + 4 < p.N) *reinterpret_cast<float4*>(prow + c0 + 4) = v1;
+                    }
+                }
             }
         }
 #pragma unroll
@@ -110,7 +120,7 @@ __device__ __forceinline__ void flush_fragment(const SpmmArgs& p, int ff, int co
 // spmm_umma.cu: tcgen05 / tensor-memory variant (SR-BCRS, N % 128 == 0, groups of at most
 // kUmmaMaxGroupTiles tiles).
 constexpr int kUmmaMaxGroupTiles = 256;
-int launch_spmm_umma(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st);
+int launch_spmm_umma(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int variant);
 
 // spmm_async.cu: shared-memory ring variant (SR-BCRS).  nq / stages 0 = defaults.
 int launch_spmm_async(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int nq, int stages);

@@ -41,6 +41,7 @@ static int g_tune_min_blocks = 0;
 static int g_tune_async = 1;   // 1 = shared-memory ring fed by cp.async (SR-BCRS), 0 = register pipeline
 static int g_tune_stages = 0;
 static int g_tune_hints = 0;
+static int g_tune_umma_variant = 0;   // 0 = slabs by N, 1 / 2 = 128-column slabs with 4 / 2 tiles per step
 static int g_tune_umma = 1;    // 1 = tcgen05 kernel where it applies (see launch_spmm), 2 = whenever N % 128 == 0
 
 template <int NQ, bool METCF, int MIN_BLOCKS>
@@ -165,9 +166,18 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, MIN_BLOCKS) spmm_mma_kern
                     v1.x = fmaxf(v1.x, 0.f); v1.y = fmaxf(v1.y, 0.f); v1.z = fmaxf(v1.z, 0.f); v1.w = fmaxf(v1.w, 0.f);
                 }
                 if (r < rows_ok) {
-                    float* row = dst + (int64_t)r * ld;
+                    float* row = (slot < 0 && p.row_map) ? p.C + (int64_t)p.row_map[w * kWinRows + r] * p.ldc
+                                                         : dst + (int64_t)r * ld;
                     if (c0 < p.N) *reinterpret_cast<float4*>(row + c0) = v0;
                     if (c0 + 4 < p.N) *reinterpret_cast<float4*>(row + c0 + 4) = v1;
+                    if (slot < 0) {  // the same row into every peer's copy of C
+                        const int64_t off = row - p.C;
+                        for (int j = 0; j < p.n_peer_out; j++) {
+                            float* prow = p.peer_out[j] + off;
+                            if (c0 < p.N) *reinterpret_cast<float4*>(prow + c0) = v0;
+                            if (c0 + 4 < p.N) *reinterpret_cast<float4*>(prow + c0 + 4) = v1;
+                        }
+                    }
                 }
             }
 #pragma unroll
@@ -239,7 +249,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, MIN_BLOCKS) spmm_mma_kern
 __global__ void __launch_bounds__(256) spmm_fixup_kernel(const int32_t* head_frag, const int32_t* frag_win,
                                                         const int32_t* frag_slot, int64_t n_frag,
                                                         const float* scratch, float* C, int64_t ldc, int32_t M,
-                                                        int32_t N, int32_t relu, const int32_t* row_map) {
+                                                        int32_t N, int32_t relu, const int32_t* row_map,
+                                                        float* const* peer_out, int32_t n_peer_out) {
     const int64_t f0 = head_frag[blockIdx.x];
     const int w = frag_win[f0];
     int64_t f1 = f0;
@@ -256,6 +267,7 @@ __global__ void __launch_bounds__(256) spmm_fixup_kernel(const int32_t* head_fra
         if (relu) { s.x = fmaxf(s.x, 0.f); s.y = fmaxf(s.y, 0.f); s.z = fmaxf(s.z, 0.f); s.w = fmaxf(s.w, 0.f); }
         const int out_row = row_map ? row_map[w * kWinRows + r] : w * kWinRows + r;
         *reinterpret_cast<float4*>(C + (int64_t)out_row * ldc + c) = s;
+        for (int j = 0; j < n_peer_out; j++) *reinterpret_cast<float4*>(peer_out[j] + (int64_t)out_row * ldc + c) = s;
     }
 }
 
@@ -263,7 +275,7 @@ static int launch_fixup(const mask_plan* plan, const SpmmArgs& a, cudaStream_t s
     if (plan->H > 0) {
         dim3 fgrid((unsigned)plan->H, (unsigned)((kWinRows * (a.N >> 2) + 255) / 256));
         spmm_fixup_kernel<<<fgrid, 256, 0, st>>>(plan->d_head_frag, plan->d_frag_win, plan->d_frag_slot, plan->F,
-                                                 a.scratch, a.C, a.ldc, a.M, a.N, a.relu, a.row_map);
+                                                 a.scratch, a.C, a.ldc, a.M, a.N, a.relu, a.row_map, a.peer_out, a.n_peer_out);
         MASK_CUDA_TRY(cudaGetLastError());
     }
     return MASK_OK;
@@ -277,6 +289,8 @@ static int launch_spmm(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
     a.frag_slot = plan->d_frag_slot;
     a.group_off = plan->d_group_off;
     a.row_map = plan->d_row_map;
+    a.peer_out = plan->d_peer_out;
+    a.n_peer_out = plan->n_peer_out;
     // columns per warp: wide slabs (fewer re-reads of the tile values per column) when N fills
     // four warps of them, else narrower slabs so that small N still spreads over a block
     const int N = a.N;
@@ -286,7 +300,7 @@ static int launch_spmm(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
     // for ME-TCF it beats the register-pipelined kernel at every width.  umma = 2 forces it.
     const bool umma_fits = N % 128 == 0 && plan->max_group_tiles <= kUmmaMaxGroupTiles;
     if (umma_fits && (g_tune_umma == 2 || (g_tune_umma == 1 && (METCF || N % 512 == 0)))) {
-        int rc = launch_spmm_umma(plan, a, st);
+        int rc = launch_spmm_umma(plan, a, st, g_tune_umma_variant);
         if (rc != MASK_OK) return rc;
         return launch_fixup(plan, a, st);
     }
@@ -347,6 +361,7 @@ extern "C" int mask_tune(const char* name, int value) {
     else if (!strcmp(name, "stages")) g_tune_stages = value;
     else if (!strcmp(name, "hints")) g_tune_hints = value;
     else if (!strcmp(name, "umma")) g_tune_umma = value;
+    else if (!strcmp(name, "umma_variant")) g_tune_umma_variant = value;
     else return fail(MASK_ERR_INVALID_ARGUMENT, "unknown tuning knob");
     return MASK_OK;
 }

@@ -49,17 +49,26 @@ constexpr int kUmmaABytes = 512;
 constexpr int kUmmaIdsBytes = kUmmaMaxGroupTiles * kTileCols * 4;
 constexpr long long kUmmaWaitCycles = 2000000000LL;
 
-// NSLAB 128-column slabs per block (N % (128*NSLAB) == 0), S ring stages.
-template <int NSLAB, int S>
+// A ring stage holds U "units" of 8 gathered rows x 128 columns (4 KB each):
+//   KB == 1: the NSLAB column slabs of ONE tile (block = 128*NSLAB columns wide),
+//   KB  > 1: the same 128-column slab of KB CONSECUTIVE tiles of one window (block = 128 columns
+//            wide; blockIdx.y walks the slabs, and because blocks are dispatched x-fastest the whole
+//            matrix is swept once per slab, so rows of B compete for L2 with 512 bytes each instead
+//            of 4N bytes -- the lever against re-reading B on power-law matrices).
+// Either way a stage is one pipeline step: one full/ready/empty round trip and U MMAs.
+template <int NSLAB, int KB, int S>
 struct UmmaLayout {
-    static constexpr int kBBytes = NSLAB * 4096;                  // gathered rows of one tile
+    static constexpr int kUnits = NSLAB * KB;
+    static constexpr int kTilesPerStep = KB;
+    static constexpr int kBBytes = kUnits * 4096;                 // gathered rows of one step
+    static constexpr int kABytes = KB * kUmmaABytes;              // tile operand(s) of one step
     static constexpr int kTmemCols = 32 * NSLAB;                  // two accumulator buffers of 16*NSLAB columns
     static constexpr int kB = 0;
     static constexpr int kA = S * kBBytes;
-    static constexpr int kIds = kA + S * kUmmaABytes;
+    static constexpr int kIds = kA + S * kABytes;
     static constexpr int kRuns = kIds + kUmmaIdsBytes;            // ME-TCF: [begin, end) of every tile's COO run
-    static constexpr int kCoo = kRuns + kUmmaMaxGroupTiles * 8;   // ME-TCF: per stage 32 idx + 32 val of the run
-    static constexpr int kBars = kCoo + S * 256;                  // full[S], empty[S], ready[S], acc_full[2], acc_empty[2]
+    static constexpr int kCoo = kRuns + kUmmaMaxGroupTiles * 8;   // ME-TCF: per stage and tile 32 idx + 32 val of the run
+    static constexpr int kBars = kCoo + S * KB * 256;             // full[S], empty[S], ready[S], acc_full[2], acc_empty[2]
     static constexpr int kTmemSlot = kBars + (3 * S + 4) * 8;
     static constexpr int kAbort = kTmemSlot + 8;
     static constexpr int kBytes = kAbort + 8;
@@ -134,23 +143,21 @@ __device__ __forceinline__ void cp16(uint32_t dst, const void* src) {
 // kernel.inc:822-840 does the same in its shared-memory restore step).  ME-TCF's index
 // Swizzle<1,2,3>(8r+c) is exactly the K-major SWIZZLE_32B operand layout, so tile[idx] = value
 // yields the operand directly, rows unpermuted.
-template <int NSLAB, int S, int MIN_BLOCKS, bool METCF>
+template <int NSLAB, int KB, int S, int MIN_BLOCKS, bool METCF>
 __global__ void __launch_bounds__(kUmmaThreads, MIN_BLOCKS) spmm_umma_kernel(const SpmmArgs p, int32_t* status) {
-    constexpr int kUmmaStages = S;
-    constexpr int kUmmaSlabs = NSLAB;
-    constexpr int kUmmaBBytes = NSLAB * 4096;
+    static_assert(KB == 1 || NSLAB == 1, "tiles are batched along K only in single-slab blocks");
+    using L = UmmaLayout<NSLAB, KB, S>;
     constexpr int kAccCols = 16 * NSLAB;                          // accumulator columns per buffer
     extern __shared__ unsigned char umma_smem_raw[];
     const uint32_t raw = (uint32_t)__cvta_generic_to_shared(umma_smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;            // swizzle patterns are functions of the address bits
     unsigned char* gbase = umma_smem_raw + (base - raw);
-    using L = UmmaLayout<NSLAB, S>;
     const uint32_t bars = base + L::kBars;
     auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (kUmmaStages + s); };
-    auto ready_bar = [&](int s) { return bars + 8u * (2 * kUmmaStages + s); };
-    auto accf_bar = [&](int b) { return bars + 8u * (3 * kUmmaStages + b); };
-    auto acce_bar = [&](int b) { return bars + 8u * (3 * kUmmaStages + 2 + b); };
+    auto empty_bar = [&](int s) { return bars + 8u * (S + s); };
+    auto ready_bar = [&](int s) { return bars + 8u * (2 * S + s); };
+    auto accf_bar = [&](int b) { return bars + 8u * (3 * S + b); };
+    auto acce_bar = [&](int b) { return bars + 8u * (3 * S + 2 + b); };
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + L::kAbort);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + L::kTmemSlot);
 
@@ -158,11 +165,11 @@ __global__ void __launch_bounds__(kUmmaThreads, MIN_BLOCKS) spmm_umma_kernel(con
     const int f0 = p.group_off[blockIdx.x], f_end = p.group_off[blockIdx.x + 1];
     const int t0 = p.frag_off[f0];
     const int n_tiles = p.frag_off[f_end] - t0;   // <= kUmmaMaxGroupTiles (checked by the launcher)
-    const int col0 = blockIdx.y * (kUmmaSlabs * 128);
+    const int col0 = blockIdx.y * (NSLAB * 128);
 
     if (tid == 0) {
         *abort_flag = 0;
-        for (int s = 0; s < kUmmaStages; s++) {
+        for (int s = 0; s < S; s++) {
             mbar_init(full_bar(s), 128);   // one deferred arrive per producer thread
             mbar_init(empty_bar(s), 1);    // tcgen05.commit
             mbar_init(ready_bar(s), 1);    // lane 0 of the preparing warp
@@ -183,7 +190,7 @@ __global__ void __launch_bounds__(kUmmaThreads, MIN_BLOCKS) spmm_umma_kernel(con
         const int pt = tid - 224;
         const int chunks = n_tiles * 2;
         for (int c = pt; c < chunks; c += 128) cp16(base + L::kIds + c * 16, p.val_sidx + (int64_t)t0 * kTileCols + c * 4);
-        if (METCF) {  // run offsets: coo_off[2t], coo_off[2t+1]; 2*t0 ints in is 8-byte aligned only, so copy by 8 bytes
+        if (METCF) {  // run offsets coo_off[2t], coo_off[2t+1]: 8-byte aligned pairs
             for (int c = pt; c < n_tiles; c += 128)
                 asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(base + L::kRuns + c * 8), "l"(p.coo_off + 2 * (int64_t)(t0 + c)) : "memory");
         }
@@ -194,74 +201,102 @@ __global__ void __launch_bounds__(kUmmaThreads, MIN_BLOCKS) spmm_umma_kernel(con
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
+    // Every role walks the same sequence of steps: for each fragment with n > 0 tiles, ceil(n/KB)
+    // steps of up to KB tiles (a step never spans two fragments: they accumulate separately).
     if (warp >= 7) {
         // ------------------------------ producers ------------------------------------------------
-        const int pw = warp - 7;                 // this warp copies 32-column atom pw of every slab
+        const int pw = warp - 7;                 // this warp copies 32-column atom pw of every unit
         const int lr = lane >> 3, lc = lane & 7; // row (and row + 4), 16-byte chunk
         const uint32_t off0 = (uint32_t)(pw * 1024 + lr * 128 + ((lc ^ (2 * lr)) * 16));   // 32-byte chunks swizzled by row % 4
         const uint32_t off1 = off0 + 512;                                                 // row + 4: same swizzle phase
         const char* Bcol = reinterpret_cast<const char*>(p.B + col0 + 32 * pw + 4 * lc);
         const uint32_t ldb_bytes = (uint32_t)(p.ldb * 4);
         const int* ids = reinterpret_cast<const int*>(gbase + L::kIds);
-        int s = 0;
+        int s = 0, rel = 0;
         uint32_t round = 0;
-        for (int rel = 0; rel < n_tiles; rel++) {
-            if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag)) break;
-            const char* r0 = Bcol + (uint64_t)(uint32_t)ids[rel * kTileCols + lr] * ldb_bytes;
-            const char* r1 = Bcol + (uint64_t)(uint32_t)ids[rel * kTileCols + lr + 4] * ldb_bytes;
-            const uint32_t dst = base + L::kB + s * kUmmaBBytes;
+        bool ok = true;
+        for (int f = f0; f < f_end && ok; f++) {
+            const int n = p.frag_off[f + 1] - p.frag_off[f];
+            for (int i = 0; i < n; i += KB) {
+                const int cnt = min(KB, n - i);
+                if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag)) { ok = false; break; }
+                const uint32_t dst = base + L::kB + s * L::kBBytes;
 #pragma unroll
-            for (int i = 0; i < kUmmaSlabs; i++) {
-                cp16(dst + i * 4096 + off0, r0 + i * 512);
-                cp16(dst + i * 4096 + off1, r1 + i * 512);
-            }
-            if (pw == 0) {
-                if (METCF) {
-                    // first 32 entries of the run (runs start on multiples of 8 entries and are padded to 8)
-                    const int2 run = reinterpret_cast<const int2*>(gbase + L::kRuns)[rel];
-                    const int chunk = lane & 7;   // 4 entries
-                    if (lane < 16 && run.x + 4 * chunk < ((run.y + 7) & ~7)) {
-                        const void* src = lane < 8 ? static_cast<const void*>(p.coo_idx + run.x + 4 * chunk)
-                                                   : static_cast<const void*>(p.coo_val + run.x + 4 * chunk);
-                        cp16(base + L::kCoo + s * 256 + lane * 16, src);
+                for (int u = 0; u < KB; u++) {
+                    if (u < cnt) {
+                        const char* r0 = Bcol + (uint64_t)(uint32_t)ids[(rel + u) * kTileCols + lr] * ldb_bytes;
+                        const char* r1 = Bcol + (uint64_t)(uint32_t)ids[(rel + u) * kTileCols + lr + 4] * ldb_bytes;
+#pragma unroll
+                        for (int sl = 0; sl < NSLAB; sl++) {
+                            cp16(dst + (u * NSLAB + sl) * 4096 + off0, r0 + sl * 512);
+                            cp16(dst + (u * NSLAB + sl) * 4096 + off1, r1 + sl * 512);
+                        }
                     }
-                } else {
-                    cp16(base + L::kA + s * kUmmaABytes + lane * 16, p.val_blk + (int64_t)(t0 + rel) * kTileElems + lane * 4);
                 }
+                // tile operand(s): warp u copies the one of tile u of the step
+                if (pw < cnt) {
+                    const int tile = rel + pw;
+                    if (METCF) {
+                        // first 32 entries of the run (runs start on multiples of 8 entries and are padded to 8)
+                        const int2 run = reinterpret_cast<const int2*>(gbase + L::kRuns)[tile];
+                        const int chunk = lane & 7;   // 4 entries
+                        if (lane < 16 && run.x + 4 * chunk < ((run.y + 7) & ~7)) {
+                            const void* src = lane < 8 ? static_cast<const void*>(p.coo_idx + run.x + 4 * chunk)
+                                                       : static_cast<const void*>(p.coo_val + run.x + 4 * chunk);
+                            cp16(base + L::kCoo + (s * KB + pw) * 256 + lane * 16, src);
+                        }
+                    } else {
+                        cp16(base + L::kA + s * L::kABytes + pw * kUmmaABytes + lane * 16,
+                             p.val_blk + (int64_t)(t0 + tile) * kTileElems + lane * 4);
+                    }
+                }
+                // arrives on full[s] once every copy this thread has issued so far has landed
+                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(full_bar(s)) : "memory");
+                rel += cnt;
+                if (++s == S) { s = 0; round++; }
             }
-            // arrives on full[s] once every copy this thread has issued so far has landed
-            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(full_bar(s)) : "memory");
-            if (++s == kUmmaStages) { s = 0; round++; }
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
     } else if (warp >= 5) {
-        // ------------------------------ prepare (two warps, alternate tiles) -------------------------
+        // ------------------------------ prepare (two warps, alternate steps) -------------------------
         const int q = warp - 5;
-        for (int rel = q; rel < n_tiles; rel += 2) {
-            const int s = rel % kUmmaStages;
-            const uint32_t round = (uint32_t)(rel / kUmmaStages);
-            if (!mbar_wait(full_bar(s), round & 1, abort_flag)) break;
-            if (METCF) {  // rebuild the 16x8 operand: zero, then tile[idx] = rna(value) over the run
-                uint32_t* tile = reinterpret_cast<uint32_t*>(gbase + L::kA + s * kUmmaABytes);
-                reinterpret_cast<uint4*>(tile)[lane] = make_uint4(0u, 0u, 0u, 0u);
-                __syncwarp();
-                const int2 run = reinterpret_cast<const int2*>(gbase + L::kRuns)[rel];
-                const int cnt = run.y - run.x;
-                const int* sidx = reinterpret_cast<const int*>(gbase + L::kCoo + s * 256);
-                const uint32_t* sval = reinterpret_cast<const uint32_t*>(gbase + L::kCoo + s * 256 + 128);
-                if (lane < cnt) tile[sidx[lane]] = sval[lane] + 0x1000u;
-                for (int e = run.x + 32 + lane; e < run.y; e += 32)   // dense tiles: entries beyond the staged 32
-                    tile[__ldg(p.coo_idx + e)] = __float_as_uint(__ldg(p.coo_val + e)) + 0x1000u;
-                __syncwarp();
-            } else if (!(p.hints & 4)) {  // round the tile values to TF32 (nearest, ties away) in place
-                uint4* at = reinterpret_cast<uint4*>(gbase + L::kA + s * kUmmaABytes) + lane;
-                uint4 v = *at;
-                v.x += 0x1000u; v.y += 0x1000u; v.z += 0x1000u; v.w += 0x1000u;
-                *at = v;
+        int s = 0, rel = 0, step = 0;
+        uint32_t round = 0;
+        bool ok = true;
+        for (int f = f0; f < f_end && ok; f++) {
+            const int n = p.frag_off[f + 1] - p.frag_off[f];
+            for (int i = 0; i < n; i += KB, step++) {
+                const int cnt = min(KB, n - i);
+                if ((step & 1) == q) {
+                    if (!mbar_wait(full_bar(s), round & 1, abort_flag)) { ok = false; break; }
+                    for (int u = 0; u < cnt; u++) {
+                        unsigned char* aslot = gbase + L::kA + s * L::kABytes + u * kUmmaABytes;
+                        if (METCF) {  // rebuild the 16x8 operand: zero, then tile[idx] = rna(value) over the run
+                            uint32_t* tile = reinterpret_cast<uint32_t*>(aslot);
+                            reinterpret_cast<uint4*>(tile)[lane] = make_uint4(0u, 0u, 0u, 0u);
+                            __syncwarp();
+                            const int2 run = reinterpret_cast<const int2*>(gbase + L::kRuns)[rel + u];
+                            const int rcnt = run.y - run.x;
+                            const int* sidx = reinterpret_cast<const int*>(gbase + L::kCoo + (s * KB + u) * 256);
+                            const uint32_t* sval = reinterpret_cast<const uint32_t*>(gbase + L::kCoo + (s * KB + u) * 256 + 128);
+                            if (lane < rcnt) tile[sidx[lane]] = sval[lane] + 0x1000u;
+                            for (int e = run.x + 32 + lane; e < run.y; e += 32)   // dense tiles: entries beyond the staged 32
+                                tile[__ldg(p.coo_idx + e)] = __float_as_uint(__ldg(p.coo_val + e)) + 0x1000u;
+                            __syncwarp();
+                        } else if (!(p.hints & 4)) {  // round the tile values to TF32 (nearest, ties away) in place
+                            uint4* at = reinterpret_cast<uint4*>(aslot) + lane;
+                            uint4 v = *at;
+                            v.x += 0x1000u; v.y += 0x1000u; v.z += 0x1000u; v.w += 0x1000u;
+                            *at = v;
+                        }
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(ready_bar(s));
+                }
+                rel += cnt;
+                if (++s == S) { s = 0; round++; }
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(ready_bar(s));
         }
     } else if (warp == 4) {
         // ------------------------------ MMA issuer (one lane) ------------------------------------------
@@ -276,17 +311,23 @@ __global__ void __launch_bounds__(kUmmaThreads, MIN_BLOCKS) spmm_umma_kernel(con
                 const uint32_t uses = buf ? uses1 : uses0;
                 if (uses > 0 && !mbar_wait(acce_bar(buf), (uses - 1) & 1, abort_flag)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                for (int i = 0; i < n; i++) {
+                for (int i = 0; i < n; i += KB) {
+                    const int cnt = min(KB, n - i);
                     if (!mbar_wait(ready_bar(s), round & 1, abort_flag)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t bdesc = umma_smem_desc(base + L::kA + s * kUmmaABytes, 1, 16, kSwizzle32B);
 #pragma unroll
-                    for (int slab = 0; slab < kUmmaSlabs; slab++) {
-                        const uint64_t adesc = umma_smem_desc(base + L::kB + s * kUmmaBBytes + slab * 4096, 64, 32, kSwizzle128B32B);
-                        umma_tf32(tmem_base + buf * kAccCols + slab * 16, adesc, bdesc, i > 0 ? 1u : 0u);
+                    for (int u = 0; u < KB; u++) {
+                        if (u < cnt) {
+                            const uint64_t bdesc = umma_smem_desc(base + L::kA + s * L::kABytes + u * kUmmaABytes, 1, 16, kSwizzle32B);
+#pragma unroll
+                            for (int sl = 0; sl < NSLAB; sl++) {
+                                const uint64_t adesc = umma_smem_desc(base + L::kB + s * L::kBBytes + (u * NSLAB + sl) * 4096, 64, 32, kSwizzle128B32B);
+                                umma_tf32(tmem_base + buf * kAccCols + sl * 16, adesc, bdesc, (i + u) > 0 ? 1u : 0u);
+                            }
+                        }
                     }
                     umma_commit(empty_bar(s));   // the slot is free once these MMAs have read it
-                    if (++s == kUmmaStages) { s = 0; round++; }
+                    if (++s == S) { s = 0; round++; }
                 }
                 if (!ok) break;
                 umma_commit(accf_bar(buf));      // accumulators of this fragment complete
@@ -304,16 +345,12 @@ __global__ void __launch_bounds__(kUmmaThreads, MIN_BLOCKS) spmm_umma_kernel(con
             const int n = p.frag_off[f + 1] - p.frag_off[f];
             const int w = p.frag_win[f];
             const int slot = p.frag_slot[f];
-            float* dst;
-            int64_t ld;
-            int rows_ok;
-            if (slot < 0) { dst = p.C + (int64_t)w * kWinRows * p.ldc; ld = p.ldc; rows_ok = p.M - w * kWinRows; }
-            else { dst = p.scratch + (int64_t)slot * kWinRows * p.N; ld = p.N; rows_ok = kWinRows; }
+            const int rows_ok = slot < 0 ? p.M - w * kWinRows : kWinRows;
             const bool relu = p.relu && slot < 0;
-            uint32_t v[kUmmaSlabs][16];
+            uint32_t v[NSLAB][16];
             if (n == 0) {
 #pragma unroll
-                for (int sl = 0; sl < kUmmaSlabs; sl++)
+                for (int sl = 0; sl < NSLAB; sl++)
 #pragma unroll
                     for (int i = 0; i < 16; i++) v[sl][i] = 0u;
             } else {
@@ -321,7 +358,7 @@ __global__ void __launch_bounds__(kUmmaThreads, MIN_BLOCKS) spmm_umma_kernel(con
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t taddr = tmem_base + ((uint32_t)(32 * warp) << 16) + buf * kAccCols;
 #pragma unroll
-                for (int sl = 0; sl < kUmmaSlabs; sl++) tmem_ld16(taddr + sl * 16, v[sl]);
+                for (int sl = 0; sl < NSLAB; sl++) tmem_ld16(taddr + sl * 16, v[sl]);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
@@ -329,16 +366,28 @@ __global__ void __launch_bounds__(kUmmaThreads, MIN_BLOCKS) spmm_umma_kernel(con
                 uses[buf]++;
                 buf ^= 1;
             }
+            if (relu) {
 #pragma unroll
-            for (int i = 0; i < 16; i++) {
-                const int r = METCF ? i : (i ^ (i >> 3));   // MMA-N index -> window row (SR-BCRS: rows 8..15 swapped pairwise)
-                if (r < rows_ok) {
-                    float* row = (slot < 0 && p.row_map) ? p.C + (int64_t)p.row_map[w * kWinRows + r] * p.ldc : dst + (int64_t)r * ld;
+                for (int sl = 0; sl < NSLAB; sl++)
 #pragma unroll
-                    for (int sl = 0; sl < kUmmaSlabs; sl++) {
-                        float x = __uint_as_float(v[sl][i]);
-                        if (relu) x = fmaxf(x, 0.f);
-                        row[col + 128 * sl] = x;
+                    for (int i = 0; i < 16; i++) v[sl][i] = __float_as_uint(fmaxf(__uint_as_float(v[sl][i]), 0.f));
+            }
+            // destination 0 is C (or the partial-tile scratch); 1.. are the peers' copies of C, which
+            // get the finished rows with plain stores over NVLink
+            const int n_dst = slot < 0 ? 1 + p.n_peer_out : 1;
+#pragma unroll 1
+            for (int d = 0; d < n_dst; d++) {
+                float* cb = slot >= 0 ? p.scratch + (int64_t)slot * kWinRows * p.N : (d == 0 ? p.C : p.peer_out[d - 1]);
+                int row0 = w * kWinRows;
+                asm volatile("" : "+r"(row0));   // keeps the 16 row offsets from being hoisted out of this loop into registers
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const int r = METCF ? i : (i ^ (i >> 3));   // MMA-N index -> window row (SR-BCRS: rows 8..15 swapped pairwise)
+                    if (r < rows_ok) {
+                        const int64_t off = slot >= 0 ? (int64_t)r * p.N
+                                                      : (int64_t)(p.row_map ? p.row_map[row0 + r] : row0 + r) * p.ldc;
+#pragma unroll
+                        for (int sl = 0; sl < NSLAB; sl++) cb[off + col + 128 * sl] = __uint_as_float(v[sl][i]);
                     }
                 }
             }
@@ -355,10 +404,10 @@ __global__ void __launch_bounds__(kUmmaThreads, MIN_BLOCKS) spmm_umma_kernel(con
     if (tid == 0 && *abort_flag) atomicExch(status, 1);
 }
 
-template <int NSLAB, int S, int MIN_BLOCKS>
+template <int NSLAB, int KB, int S, int MIN_BLOCKS>
 static int launch_umma_variant(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st) {
-    using L = UmmaLayout<NSLAB, S>;
-    auto kern = a.coo_off ? spmm_umma_kernel<NSLAB, S, MIN_BLOCKS, true> : spmm_umma_kernel<NSLAB, S, MIN_BLOCKS, false>;
+    using L = UmmaLayout<NSLAB, KB, S>;
+    auto kern = a.coo_off ? spmm_umma_kernel<NSLAB, KB, S, MIN_BLOCKS, true> : spmm_umma_kernel<NSLAB, KB, S, MIN_BLOCKS, false>;
     MASK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));
     dim3 grid((unsigned)plan->G, (unsigned)(a.N / (NSLAB * 128)));
     if (grid.y > 65535) return fail(MASK_ERR_INVALID_ARGUMENT, "N too large");
@@ -367,13 +416,16 @@ static int launch_umma_variant(const mask_plan* plan, const SpmmArgs& a, cudaStr
     return MASK_OK;
 }
 
-int launch_spmm_umma(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st) {
+// variant: 0 = by N (widest slab group that divides N: the tile values and ids are fetched once per
+// block), 1 = 128-column slabs with 4 tiles per pipeline step (sweeps the matrix once per slab)
+int launch_spmm_umma(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int variant) {
     if (a.N % 128 != 0) return fail(MASK_ERR_INVALID_ARGUMENT, "the tcgen05 kernel needs N % 128 == 0");
     if (plan->max_group_tiles > kUmmaMaxGroupTiles) return fail(MASK_ERR_INVALID_ARGUMENT, "plan groups too large for the tcgen05 kernel");
-    // widest slab group that divides N: the tile values and ids are fetched once per block
-    if (a.N % 512 == 0) return launch_umma_variant<4, 6, 2>(plan, a, st);
-    if (a.N % 256 == 0) return launch_umma_variant<2, 8, 2>(plan, a, st);
-    return launch_umma_variant<1, 8, 3>(plan, a, st);
+    if (variant == 1) return launch_umma_variant<1, 4, 5, 2>(plan, a, st);
+    if (variant == 2) return launch_umma_variant<1, 2, 8, 2>(plan, a, st);
+    if (a.N % 512 == 0) return launch_umma_variant<4, 1, 6, 2>(plan, a, st);
+    if (a.N % 256 == 0) return launch_umma_variant<2, 1, 8, 2>(plan, a, st);
+    return launch_umma_variant<1, 1, 8, 3>(plan, a, st);
 }
 
 }  // namespace mask

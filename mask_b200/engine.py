@@ -66,6 +66,16 @@ class Plan:
         check(lib().mask_plan_status(self._h, C.byref(v), _stream()), "mask_plan_status")
         return int(v.value)
 
+    def set_peer_outputs(self, ptrs: torch.Tensor | None) -> None:
+        """ptrs: int64 CUDA tensor of device addresses (bases of the peers' copies of C), or None."""
+        if ptrs is None:
+            check(lib().mask_plan_set_peer_outputs(self._h, None, 0), "mask_plan_set_peer_outputs")
+            self._peer_ptrs = None
+            return
+        _req(ptrs, torch.int64, "ptrs")
+        check(lib().mask_plan_set_peer_outputs(self._h, _ptr(ptrs), int(ptrs.numel())), "mask_plan_set_peer_outputs")
+        self._peer_ptrs = ptrs  # keep the array alive as long as the plan uses it
+
     def export(self):
         """Host copies of (frag_offset[F+1], frag_window[F], group_offset[G+1])."""
         i = self.info()

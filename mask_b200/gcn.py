@@ -114,6 +114,62 @@ class ShardedGCN2:
         return torch.cat(outs, dim=0) if outs else Z.new_zeros((0, Z.shape[1]))
 
 
+class FusedGCN2:
+    """The same forward with the exchange fused into the layer-1 SpMM: its epilogue stores every
+    finished row of ``H1 = ReLU(A·XW1)`` into all ranks' copies of H1 (peer-mapped buffers, plain
+    stores over NVLink) while the product is still running, so there is no collective on the data
+    path, only a one-word all-reduce as the barrier between the layers.  Layer 2 is reassociated,
+    ``out = (A·H1)·W2``, so that what the SpMM produces is what the peers need.
+
+    H1 is double-buffered: a rank that races ahead into the next forward writes the other buffer,
+    and cannot get a second forward ahead because of the barrier, so no rank's layer-2 reads are
+    overwritten."""
+
+    def __init__(self, csr, rank: int, world: int, device, win_prefix, hidden: int, group=None):
+        from . import engine
+        from .peer import PeerBuffer
+        self.engine = engine
+        self.M, self.K, self.rank, self.world, self.group = csr.M, csr.K, rank, world, group
+        if csr.M != csr.K:
+            raise RuntimeError("the GCN forward needs a square adjacency matrix")
+        self.bounds = balanced_panels(np.asarray(win_prefix), csr.M, world)
+        self.r0, self.r1 = self.bounds[rank], self.bounds[rank + 1]
+        pack, _ = device_ops(device)
+        self.packed = pack(csr.row_slice(self.r0, self.r1)) if self.r1 > self.r0 else None
+        self.hidden = hidden
+        self.h1 = [PeerBuffer((csr.M, hidden), device, rank, world, group) for _ in range(2)]
+        self.plans = []
+        if self.packed is not None:
+            for b in self.h1:
+                plan = self.packed.new_plan()
+                if world > 1:
+                    plan.set_peer_outputs(b.others(self.r0 * hidden * 4))
+                self.plans.append(plan)
+        self.flag = torch.zeros(1, dtype=torch.int32, device=device)
+        self.step = 0
+
+    def forward(self, X: torch.Tensor, W1: torch.Tensor, W2: torch.Tensor) -> torch.Tensor:
+        """Returns this rank's rows [bounds[rank], bounds[rank+1]) of the output."""
+        if W1.shape[1] != self.hidden:
+            raise RuntimeError("W1 does not match the hidden width this object was built for")
+        XW1 = X @ W1
+        b = self.step & 1
+        self.step += 1
+        h1 = self.h1[b].local
+        if self.packed is not None:
+            self.engine.spmm(self.packed, XW1, out=h1[self.r0:self.r1], relu=True, plan=self.plans[b])
+        if self.world > 1:
+            dist.all_reduce(self.flag, group=self.group)   # stream-ordered barrier: every panel of H1 has landed
+        if self.packed is None:
+            return X.new_zeros((0, W2.shape[1]))
+        return self.engine.spmm(self.packed, h1) @ W2
+
+    def close(self) -> None:
+        self.plans = []
+        for b in self.h1:
+            b.close()
+
+
 class _null:
     def __enter__(self):
         return self

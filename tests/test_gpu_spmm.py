@@ -233,7 +233,8 @@ def test_medium_rmat_against_oracle(oracle_mod):
                                        ("rmat12u", 512, 200), ("stencil8", 1024, 0), ("three_four_tiles", 512, 1),
                                        ("rmat12u", 128, 0), ("hub_rows", 256, 3), ("rmat10", 384, 0), ("m17", 768, 0),
                                        ("m33_empty_window", 128, 0), ("stencil8", 256, 0)])
-def test_srbcrs_spmm_tcgen05_kernel(oracle_mod, name, N, gt):
+@pytest.mark.parametrize("variant", [0, 1, 2])
+def test_srbcrs_spmm_tcgen05_kernel(oracle_mod, name, N, gt, variant):
     """The tcgen05 / tensor-memory kernel (N a multiple of 128; 1, 2 or 4 slabs per block): same contract, its bounded waits
     must not have expired, and results are deterministic.  Operand B is truncated to TF32 by the
     tensor core (the tile values are rounded), which stays inside the product tolerance."""
@@ -245,14 +246,63 @@ def test_srbcrs_spmm_tcgen05_kernel(oracle_mod, name, N, gt):
     B = _dense(m.K, N, 41)
     Bd = torch.from_numpy(B).cuda()
     plan = engine.Plan(p.val_soff, m.M, p.T, "auto", gt)
+    pm = engine.pack_metcf(rp, ci, va, m.M, m.K)
     try:
         engine.tune("umma", 2)
+        engine.tune("umma_variant", variant)   # slabs by N / 128-column slabs with 4 or 2 tiles per step
         out = torch.full((m.M, N), float("nan"), device="cuda")
         engine.spmm(p, Bd, out=out, plan=plan)
         out2 = torch.full((m.M, N), float("nan"), device="cuda")
         engine.spmm(p, Bd, out=out2, plan=plan, relu=True)
+        out3 = torch.full((m.M, N), float("nan"), device="cuda")
+        engine.spmm(pm, Bd, out=out3, plan=plan)   # ME-TCF through the same kernel family
+    finally:
+        engine.tune("umma", 1)
+        engine.tune("umma_variant", 0)
+    assert plan.status() == 0
+    _assert_close(oracle_mod, m, B, out.cpu().numpy())
+    _assert_close(oracle_mod, m, B, out3.cpu().numpy())
+    assert torch.equal(torch.relu(out), out2)
+
+
+@pytest.mark.parametrize("name,N,gt,umma,fmt,reorder", [
+    ("rmat12u", 64, 0, 1, "srbcrs", "none"),       # cp.async ring kernel
+    ("hub_rows", 64, 3, 1, "srbcrs", "none"),      # split windows: fix-up kernel writes the rows
+    ("rmat12u", 512, 0, 2, "srbcrs", "none"),      # tcgen05 kernel, 4 slabs
+    ("hub_rows", 128, 3, 2, "srbcrs", "none"),     # tcgen05 kernel + fix-up
+    ("m17", 40, 0, 1, "metcf", "none"),            # register kernel, ragged last window
+    ("rmat10", 64, 0, 1, "srbcrs", "row_rcm"),     # rows scattered back through the row map
+])
+def test_peer_outputs_receive_the_same_rows(oracle_mod, name, N, gt, umma, fmt, reorder):
+    """mask_plan_set_peer_outputs: every extra output base gets exactly the rows C gets (here the
+    'peers' are two more buffers on the same GPU; across GPUs they are peer-mapped addresses)."""
+    import torch
+    from mask_b200 import engine, _lib
+    m = cases.SMALL[name]()
+    rp, ci, va = _dev(m)
+    if fmt == "metcf":
+        p = engine.pack_metcf(rp, ci, va, m.M, m.K)
+        plan = engine.Plan(p.val_soff, m.M, p.T, "auto", gt)
+    else:
+        p = engine.pack_srbcrs(rp, ci, va, m.M, m.K, reorder=reorder)
+        plan = p.new_plan("auto", gt)
+    B = _dense(m.K, N, 43)
+    Bd = torch.from_numpy(B).cuda()
+    out = torch.full((m.M, N), float("nan"), device="cuda")
+    peers = [torch.full((m.M, N), float("nan"), device="cuda") for _ in range(2)]
+    ptrs = torch.tensor([t.data_ptr() for t in peers], dtype=torch.int64, device="cuda")
+    try:
+        engine.tune("umma", umma)
+        plan.set_peer_outputs(ptrs)
+        engine.spmm(p, Bd, out=out, plan=plan, relu=True)
+        plan.set_peer_outputs(None)
+        plain = torch.full((m.M, N), float("nan"), device="cuda")
+        engine.spmm(p, Bd, out=plain, plan=plan, relu=True)
     finally:
         engine.tune("umma", 1)
     assert plan.status() == 0
-    _assert_close(oracle_mod, m, B, out.cpu().numpy())
-    assert torch.equal(torch.relu(out), out2)
+    assert torch.equal(out, plain)
+    for t in peers:
+        assert torch.equal(t, out)
+    with pytest.raises(_lib.MaskError):
+        plan.set_peer_outputs(torch.zeros(16, dtype=torch.int64, device="cuda"))

@@ -110,7 +110,16 @@ def _gpu_rank_main(rank, world, port, q):
         net = ShardedGCN2(m, rank, world, pack, spmm, win_prefix=tile_prefix_on_device(m, dev), chunks=3)
         out = net.forward(X, W1, W2)
         torch.cuda.synchronize()
-        q.put((rank, net.bounds, out.cpu().numpy()))
+        # the same forward with the exchange fused into the SpMM epilogue (peer stores); three
+        # forwards so that both H1 buffers and the reuse of the first are exercised
+        from mask_b200.gcn import FusedGCN2, cost_prefix_on_device
+        fused = FusedGCN2(m, rank, world, dev, cost_prefix_on_device(m, dev), hidden=64)
+        outs = [fused.forward(X * s, W1, W2) for s in (1.0, 2.0, 1.0)]
+        torch.cuda.synchronize()
+        assert torch.equal(outs[0], outs[2]) and not torch.equal(outs[0], outs[1])
+        assert all(p.status() == 0 for p in fused.plans)
+        q.put((rank, net.bounds, out.cpu().numpy(), fused.bounds, outs[2].cpu().numpy()))
+        fused.close()
     finally:
         dist.destroy_process_group()
 
@@ -153,7 +162,27 @@ def test_gcn_forward_two_gpus():
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
-    full = np.zeros_like(want)
-    for rank, bounds, out in got:
+    full, full_fused = np.zeros_like(want), np.zeros_like(want)
+    for rank, bounds, out, fbounds, fout in got:
         full[bounds[rank]:bounds[rank + 1]] = out
+        full_fused[fbounds[rank]:fbounds[rank + 1]] = fout
     assert np.abs(full - want).max() <= 4e-3 * np.abs(want).max() + 1e-6
+    assert np.abs(full_fused - want).max() <= 4e-3 * np.abs(want).max() + 1e-6
+
+
+@pytest.mark.gpu
+def test_fused_gcn_forward_single_gpu():
+    """FusedGCN2 with one rank: library-allocated H1 buffers, reassociated layer 2."""
+    from mask_b200.gcn import FusedGCN2, cost_prefix_on_device
+    dev = torch.device("cuda", 0)
+    m = G.rmat_gcn_normalised(scale=12, samples_per_node=8, seed=501)
+    X, W1, W2 = G.dense_normal(m.K, 64, 502), G.glorot_uniform(64, 64, 503), G.glorot_uniform(64, 32, 504)
+    net = FusedGCN2(m, 0, 1, dev, cost_prefix_on_device(m, dev), hidden=64)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    args = [torch.from_numpy(a).to(dev) for a in (X, W1, W2)]
+    out = net.forward(*args).cpu().numpy()
+    out2 = net.forward(*args).cpu().numpy()
+    net.close()
+    want = _gcn_reference(m, X, W1, W2)
+    assert np.abs(out - want).max() <= 4e-3 * np.abs(want).max() + 1e-6
+    assert np.array_equal(out, out2)
