@@ -248,6 +248,46 @@ def run_gcn(args, m, bseed, dev, rank, world):
         dist.destroy_process_group()
 
 
+def run_bridge(args, m):
+    """Same-box comparison at the reference's Format-DSL bridge seam: the reference's own bridge
+    executable (its packer, its timing loop, its cuSPARSE check) built once with the operator its
+    compiler emits and once with the hand-written sm_100a operator include; both are made by
+    `make -C oracle bridge` where a checkout of the reference is present.  The bridge reads a
+    MatrixMarket file, so the workload's pattern is written to a temporary one."""
+    import subprocess
+    import tempfile
+    from mask_b200 import generators as G
+    here = os.path.dirname(os.path.abspath(__file__))
+    runs = [("reference_emitted_operator_tile64", "bridge_refgen_tn64"), ("sm100_operator_tile64", "bridge_sm100_tn64"),
+            ("sm100_operator_tile128", "bridge_sm100_tn128")]
+    out = {}
+    with tempfile.TemporaryDirectory() as tmp:
+        mtx = os.path.join(tmp, "w.mtx")
+        G.write_matrix_market(m, mtx)
+        for label, exe in runs:
+            path = os.path.join(here, "oracle", "_ref", exe)
+            if not os.path.exists(path):
+                out[label] = {"unavailable": "not built (needs a checkout of the reference)"}
+                continue
+            out[label] = {}
+            for policy in ("row", "strict_lb"):
+                js = os.path.join(tmp, "r.json")
+                cmd = [path, "--filename", mtx, "--dataset", args.workload, "--result-json", js, "--n", str(args.n), "--warmup",
+                       str(max(args.warmup, 3)), "--repeat", str(args.steps), "--execution-policy", policy]
+                r = subprocess.run(cmd, capture_output=True, text=True)
+                if r.returncode not in (0, 2) or not os.path.exists(js):
+                    out[label][policy] = {"error": (r.stderr or r.stdout)[-200:]}
+                    continue
+                rep = json.load(open(js))
+                ms = rep["timing"]["generated_ms"]
+                out[label][policy] = {"ms": ms, "gflops": 2.0 * m.nnz * args.n / (ms * 1e-3) / 1e9,
+                                      "cusparse_ms": rep["timing"]["cusparse_ms"], "passed": rep["correctness"]["passed"],
+                                      "max_abs_error": rep["correctness"]["max_abs_error"], "tiles": rep["packed"]["tiles"]}
+                os.remove(js)
+    print(json.dumps({"metric": "SpMM through the reference's Format-DSL bridge executable, kernel ms", "unit": "ms", "n_gpus": 1,
+                      "config": {"workload": args.workload, "M": m.M, "nnz": m.nnz, "N": args.n}, "bridge": out}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -267,6 +307,8 @@ def main():
     ap.add_argument("--min-blocks", type=int, default=0, help="kernel variant: occupancy target (0 = default)")
     ap.add_argument("--stages", type=int, default=0, help="kernel variant: ring slots per warp (0 = default)")
     ap.add_argument("--no-async", action="store_true", help="use the register-pipelined kernel")
+    ap.add_argument("--bridge", action="store_true",
+                    help="time the reference's Format-DSL bridge executable with its emitted operator and with the sm_100a one (extra line)")
     ap.add_argument("--gcn-fused", action="store_true", help="with --gcn: layer-1 SpMM stores H1 straight into every rank's copy")
     ap.add_argument("--gcn", action="store_true", help="time the row-sharded 2-layer GCN forward instead (extra line)")
     ap.add_argument("--baselines", action="store_true",
@@ -304,6 +346,8 @@ def main():
     dev = torch.device("cuda", local)
     if args.gcn:
         return run_gcn(args, m, bseed, dev, rank, world)
+    if args.bridge:
+        return run_bridge(args, m) if rank == 0 else None
     bounds = panel_bounds(m, world, dev)
     r0, r1 = bounds[rank], bounds[rank + 1]
     panel = m.row_slice(r0, r1) if world > 1 else m

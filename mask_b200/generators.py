@@ -187,3 +187,15 @@ def check_csr(csr: CSR) -> None:
         row_start = np.zeros(ci.shape[0], dtype=bool)
         row_start[rp[1:-1][rp[1:-1] < ci.shape[0]]] = True
         assert np.all(asc | row_start[1:]), "rows must be strictly ascending"
+
+
+def write_matrix_market(csr: CSR, path: str) -> None:
+    """Writes the sparsity pattern as a MatrixMarket ``coordinate pattern general`` file (1-based,
+    row-major order): the input format of the reference's testbeds and of its Format-DSL host
+    bridge, which assign their own deterministic values to the entries."""
+    rows = np.repeat(np.arange(csr.M, dtype=np.int64), np.diff(csr.rowptr)) + 1
+    cols = csr.colind.astype(np.int64) + 1
+    with open(path, "w") as f:
+        f.write("%%MatrixMarket matrix coordinate pattern general\n")
+        f.write(f"{csr.M} {csr.K} {csr.nnz}\n")
+        np.savetxt(f, np.stack([rows, cols], axis=1), fmt="%d")
