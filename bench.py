@@ -259,7 +259,9 @@ def run_bridge(args, m):
     from mask_b200 import generators as G
     here = os.path.dirname(os.path.abspath(__file__))
     runs = [("reference_emitted_operator_tile64", "bridge_refgen_tn64"), ("sm100_operator_tile64", "bridge_sm100_tn64"),
-            ("sm100_operator_tile128", "bridge_sm100_tn128")]
+            ("sm100_operator_tile128", "bridge_sm100_tn128"),
+            ("reference_emitted_operator_tile64_fast_tf32", "bridge_refgen_fast_tn64"),
+            ("sm100_operator_tile64_fast_tf32", "bridge_sm100_fast_tn64")]
     out = {}
     with tempfile.TemporaryDirectory() as tmp:
         mtx = os.path.join(tmp, "w.mtx")
