@@ -417,12 +417,15 @@ static int launch_umma_variant(const mask_plan* plan, const SpmmArgs& a, cudaStr
 }
 
 // variant: 0 = by N (widest slab group that divides N: the tile values and ids are fetched once per
-// block), 1 = 128-column slabs with 4 tiles per pipeline step (sweeps the matrix once per slab)
+// block), 1 / 2 / 3 = 128-column slabs with 4 / 2 / 1 tiles per pipeline step (the matrix is swept
+// once per slab), 4 = 256-column slabs
 int launch_spmm_umma(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int variant) {
     if (a.N % 128 != 0) return fail(MASK_ERR_INVALID_ARGUMENT, "the tcgen05 kernel needs N % 128 == 0");
     if (plan->max_group_tiles > kUmmaMaxGroupTiles) return fail(MASK_ERR_INVALID_ARGUMENT, "plan groups too large for the tcgen05 kernel");
     if (variant == 1) return launch_umma_variant<1, 4, 5, 2>(plan, a, st);
     if (variant == 2) return launch_umma_variant<1, 2, 8, 2>(plan, a, st);
+    if (variant == 3) return launch_umma_variant<1, 1, 8, 3>(plan, a, st);                     // 128-column slabs, one tile per step
+    if (variant == 4 && a.N % 256 == 0) return launch_umma_variant<2, 1, 8, 2>(plan, a, st);   // 256-column slabs
     if (a.N % 512 == 0) return launch_umma_variant<4, 1, 6, 2>(plan, a, st);
     if (a.N % 256 == 0) return launch_umma_variant<2, 1, 8, 2>(plan, a, st);
     return launch_umma_variant<1, 1, 8, 3>(plan, a, st);
