@@ -303,6 +303,7 @@ def main():
     ap.add_argument("--policy", default="auto")
     ap.add_argument("--group-tiles", type=int, default=0)
     ap.add_argument("--hints", type=int, default=0, help="kernel variant: L2 eviction hints bitmask")
+    ap.add_argument("--session-chunk", type=int, default=-1, help="columns per chunk of the host-buffer pipeline (-1 automatic, 0 off)")
     ap.add_argument("--umma-variant", type=int, default=0, help="tcgen05 kernel: 0 = slabs by N, 1/2/3 = 128-column slabs (4/2/1 tiles per step), 4 = 256-column slabs")
     ap.add_argument("--umma", type=int, default=1, help="1 = tcgen05 / tensor-memory kernel where it applies, 0 = mma.sync kernels")
     ap.add_argument("--e2e-steps", type=int, default=3, help="0 skips the host-buffer leg")
@@ -344,6 +345,7 @@ def main():
     engine.tune("hints", args.hints)
     engine.tune("umma", args.umma)
     engine.tune("umma_variant", args.umma_variant)
+    engine.tune("session_chunk", args.session_chunk)
     engine.tune("async", 0 if args.no_async else 1)
 
     m, bseed = build_workload(args.workload, args.scale)

@@ -276,8 +276,13 @@ int mask_spmm_srbcrs_static_scratch(const mask_plan* plan, const int32_t* d_val_
                                     int32_t M, int32_t K, int32_t N, const float* d_B, int64_t ldb,
                                     float* d_C, int64_t ldc, int epilogue, void* stream);
 
-/* Development knob for kernel variants, process-wide: "nq" (32-column groups per warp: 1, 2, 4;
- * 0 = chosen from N) and "min_blocks" (occupancy target of the variant; 0 = default).  Replaces
+/* Development knobs for kernel variants, process-wide: "nq" (32-column groups per warp: 1, 2, 4;
+ * 0 = chosen from N), "min_blocks" (occupancy target of the variant; 0 = default), "async" (0 =
+ * register-pipelined kernel instead of the cp.async ring), "stages" (ring depth variant), "hints"
+ * (bit 0: L2 eviction priorities, bit 1: streaming stores of C, bit 2: skip the rounding of tile
+ * values), "umma" (0 = never the tcgen05 kernel, 1 = where it wins, 2 = wherever it fits),
+ * "umma_variant" (0 = slabs by N, 1/2/3 = 128-column slabs with 4/2/1 tiles per step, 4 =
+ * 256-column slabs), "session_chunk" (columns per chunk of mask_session_spmm_host).  Replaces
  * the reference's tile_b environment switches SRBCRS_TILE_B / DTC_TILE_B
  * (examples/src_fp32/sr_bcrs/testbed/SRBCRSSpMM_kernel.cu:435-475). */
 int mask_tune(const char* name, int value);
@@ -299,7 +304,10 @@ int mask_session_create_csr(int32_t M, int32_t K, int64_t nnz, const int32_t* h_
                             const int32_t* h_colind, const float* h_values, int policy,
                             mask_session** out);
 /* C_host[M,N] = A * B_host[K,N]; pinned host buffers make the copies asynchronous.  kernel_ms,
- * if not NULL, receives the device time of the SpMM kernels alone. */
+ * if not NULL, receives the device time of the SpMM kernels alone.  When N is a multiple of 128
+ * and at least 256 the product is cut into column chunks (independent products) whose upload,
+ * multiplication and download overlap on three streams, so both directions of the host link are
+ * busy at once; mask_tune("session_chunk", columns | 0 = off | -1 = automatic) overrides. */
 int mask_session_spmm_host(mask_session* s, const float* h_B, float* h_C, int32_t N,
                            float* kernel_ms);
 int64_t mask_session_tiles(const mask_session* s);

@@ -51,15 +51,40 @@ struct mask_session {
     size_t b_bytes = 0, c_bytes = 0;
     cudaStream_t stream = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    // column-chunk pipeline of mask_session_spmm_host: upload, multiply and download on three streams
+    static constexpr int kMaxChunks = 8;
+    cudaStream_t up = nullptr, down = nullptr;
+    cudaEvent_t uploaded[kMaxChunks] = {}, k0[kMaxChunks] = {}, k1[kMaxChunks] = {}, downloaded = nullptr;
 };
 
 namespace mask {
+
+// -1 = automatic (128-column chunks), 0 = no chunking, else columns per chunk (mask_tune "session_chunk")
+int g_session_chunk_cols = -1;
 
 static int session_common_init(mask_session* s) {
     MASK_CUDA_TRY(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking));
     MASK_CUDA_TRY(cudaEventCreate(&s->ev0));
     MASK_CUDA_TRY(cudaEventCreate(&s->ev1));
+    MASK_CUDA_TRY(cudaStreamCreateWithFlags(&s->up, cudaStreamNonBlocking));
+    MASK_CUDA_TRY(cudaStreamCreateWithFlags(&s->down, cudaStreamNonBlocking));
+    for (int i = 0; i < mask_session::kMaxChunks; i++) {
+        MASK_CUDA_TRY(cudaEventCreateWithFlags(&s->uploaded[i], cudaEventDisableTiming));
+        MASK_CUDA_TRY(cudaEventCreate(&s->k0[i]));
+        MASK_CUDA_TRY(cudaEventCreate(&s->k1[i]));
+    }
+    MASK_CUDA_TRY(cudaEventCreateWithFlags(&s->downloaded, cudaEventDisableTiming));
     return MASK_OK;
+}
+
+// Columns per chunk of the host-buffer pipeline: a multiple of 128 that gives 2..kMaxChunks chunks,
+// or 0 when N is too narrow or ragged to be worth cutting.
+static int session_chunk_cols(int32_t N) {
+    if (g_session_chunk_cols == 0 || N % 128 != 0 || N < 256) return 0;
+    int w = g_session_chunk_cols > 0 ? g_session_chunk_cols : 128;
+    if (w % 32 != 0 || N % w != 0) w = 128;
+    while (N / w > mask_session::kMaxChunks) w *= 2;
+    return (N % w == 0 && N / w >= 2) ? w : 0;
 }
 
 static int grow(void** p, size_t* have, size_t need) {
@@ -86,6 +111,14 @@ extern "C" void mask_session_destroy(mask_session* s) {
     mask_plan_destroy(s->plan);
     if (s->ev0) cudaEventDestroy(s->ev0);
     if (s->ev1) cudaEventDestroy(s->ev1);
+    if (s->up) { cudaStreamSynchronize(s->up); cudaStreamDestroy(s->up); }
+    if (s->down) { cudaStreamSynchronize(s->down); cudaStreamDestroy(s->down); }
+    for (int i = 0; i < mask_session::kMaxChunks; i++) {
+        if (s->uploaded[i]) cudaEventDestroy(s->uploaded[i]);
+        if (s->k0[i]) cudaEventDestroy(s->k0[i]);
+        if (s->k1[i]) cudaEventDestroy(s->k1[i]);
+    }
+    if (s->downloaded) cudaEventDestroy(s->downloaded);
     if (s->stream) cudaStreamDestroy(s->stream);
     delete s;
 }
@@ -183,6 +216,41 @@ extern "C" int mask_session_spmm_host(mask_session* s, const float* h_B, float* 
     if (rc == MASK_OK) rc = grow((void**)&s->d_C, &s->c_bytes, cb);
     if (rc == MASK_OK) rc = grow(&s->d_scratch, &s->scratch_bytes, mask_plan_scratch_bytes(s->plan, N));
     if (rc != MASK_OK) return rc;
+    // Column chunks are independent products, so the upload of chunk i+1, the SpMM of chunk i and the
+    // download of chunk i-1 overlap: the link carries both directions at once and the call costs
+    // about (1 + 1/chunks) of one direction instead of both in sequence.
+    const int w = session_chunk_cols(N);
+    if (w > 0) {
+        const int chunks = N / w;
+        const size_t pitch = (size_t)N * 4, width = (size_t)w * 4;
+        for (int i = 0; i < chunks; i++) {
+            const size_t c0 = (size_t)i * w;
+            MASK_CUDA_TRY(cudaMemcpy2DAsync(s->d_B + c0, pitch, h_B + c0, pitch, width, (size_t)s->K, cudaMemcpyHostToDevice, s->up));
+            MASK_CUDA_TRY(cudaEventRecord(s->uploaded[i], s->up));
+            MASK_CUDA_TRY(cudaStreamWaitEvent(s->stream, s->uploaded[i], 0));
+            MASK_CUDA_TRY(cudaEventRecord(s->k0[i], s->stream));
+            rc = mask_spmm_srbcrs(s->plan, s->d_soff, s->d_sidx, s->d_blk, s->M, s->K, w, s->d_B + c0, N, s->d_C + c0, N,
+                                  s->d_scratch, s->scratch_bytes, MASK_EPILOGUE_NONE, s->stream);
+            if (rc != MASK_OK) break;
+            MASK_CUDA_TRY(cudaEventRecord(s->k1[i], s->stream));
+            MASK_CUDA_TRY(cudaStreamWaitEvent(s->down, s->k1[i], 0));
+            MASK_CUDA_TRY(cudaMemcpy2DAsync(h_C + c0, pitch, s->d_C + c0, pitch, width, (size_t)s->M, cudaMemcpyDeviceToHost, s->down));
+        }
+        // everything that was enqueued must finish before the caller's buffers are touched again
+        cudaError_t e1 = cudaStreamSynchronize(s->up), e2 = cudaStreamSynchronize(s->stream), e3 = cudaStreamSynchronize(s->down);
+        if (rc != MASK_OK) return rc;
+        MASK_CUDA_TRY(e1);
+        MASK_CUDA_TRY(e2);
+        MASK_CUDA_TRY(e3);
+        if (kernel_ms) {
+            for (int i = 0; i < chunks; i++) {
+                float ms = 0.f;
+                MASK_CUDA_TRY(cudaEventElapsedTime(&ms, s->k0[i], s->k1[i]));
+                *kernel_ms += ms;
+            }
+        }
+        return MASK_OK;
+    }
     MASK_CUDA_TRY(cudaMemcpyAsync(s->d_B, h_B, bb, cudaMemcpyHostToDevice, s->stream));
     MASK_CUDA_TRY(cudaEventRecord(s->ev0, s->stream));
     rc = mask_spmm_srbcrs(s->plan, s->d_soff, s->d_sidx, s->d_blk, s->M, s->K, N, s->d_B, N, s->d_C, N, s->d_scratch,

@@ -41,6 +41,7 @@ static int g_tune_min_blocks = 0;
 static int g_tune_async = 1;   // 1 = shared-memory ring fed by cp.async (SR-BCRS), 0 = register pipeline
 static int g_tune_stages = 0;
 static int g_tune_hints = 0;
+extern int g_session_chunk_cols;      // api.cu: column chunks of the host-buffer pipeline
 static int g_tune_umma_variant = 0;   // 0 = slabs by N, 1 / 2 = 128-column slabs with 4 / 2 tiles per step
 static int g_tune_umma = 1;    // 1 = tcgen05 kernel where it applies (see launch_spmm), 2 = whenever N % 128 == 0
 
@@ -362,6 +363,7 @@ extern "C" int mask_tune(const char* name, int value) {
     else if (!strcmp(name, "hints")) g_tune_hints = value;
     else if (!strcmp(name, "umma")) g_tune_umma = value;
     else if (!strcmp(name, "umma_variant")) g_tune_umma_variant = value;
+    else if (!strcmp(name, "session_chunk")) g_session_chunk_cols = value;
     else return fail(MASK_ERR_INVALID_ARGUMENT, "unknown tuning knob");
     return MASK_OK;
 }

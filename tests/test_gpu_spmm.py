@@ -207,9 +207,21 @@ def test_session_host_buffers(oracle_mod):
         out = np.full((m.M, 64), np.nan, dtype=np.float32)
         ms = C.c_float()
         _lib.check(L.mask_session_spmm_host(h, B.ctypes.data, out.ctypes.data, 64, C.byref(ms)), "spmm_host")
-        L.mask_session_destroy(h)
         assert ms.value > 0
         _assert_close(oracle_mod, m, B, out)
+        # wide products go through the column-chunk pipeline (upload / multiply / download overlapped);
+        # with chunking switched off the same call gives the same product
+        B2 = _dense(m.K, 512, 5)
+        outs = []
+        for chunk in (-1, 256, 0):
+            _lib.check(L.mask_tune(b"session_chunk", chunk), "tune")
+            o = np.full((m.M, 512), np.nan, dtype=np.float32)
+            _lib.check(L.mask_session_spmm_host(h, B2.ctypes.data, o.ctypes.data, 512, C.byref(ms)), "spmm_host")
+            assert ms.value > 0
+            _assert_close(oracle_mod, m, B2, o)
+            outs.append(o)
+        _lib.check(L.mask_tune(b"session_chunk", -1), "tune")
+        L.mask_session_destroy(h)
 
 
 def test_medium_rmat_against_oracle(oracle_mod):
