@@ -91,6 +91,24 @@ int mask_metcf_fill(const int32_t* d_rowptr, const int32_t* d_colind, const floa
                     int64_t nnz_pad, int32_t* d_val_sidx, int32_t* d_val_coo_idx,
                     float* d_val_coo_val, void* stream);
 
+/* MCO / BIT-TCF (bitmap leaf): the tiling and val_sidx of SR-BCRS (window tail padded with the last
+ * real column); per tile two 64-bit mask words, bit Swizzle<1,2,3>(8r+c) set for a stored entry,
+ * and the entries' values in ascending bit order, each tile's run padded with zeros to a multiple
+ * of 4; val_mco_off[T+1] = start of every tile's run.  Replaces the host packers
+ * examples/src_fp32/acc/testbed/main.cu:300-383 (BIT-TCF testbed; skip_zero_values = 0: explicit
+ * zeros are stored) and the Format-DSL bridge's "column_condensed" mode
+ * (examples/src_fp32/acc/testbed/custom_format_e2e.cu:527-552; skip_zero_values = 1).  After
+ * mask_pack_analyze with the same scratch.  Step 1 writes val_mco_mask[2T] and val_mco_off[T+1]
+ * and returns the total value count through *h_nval (synchronises); step 2 writes val_sidx[8T]
+ * and val_mco_val[nval].  d_values may be NULL (every entry 1.0f). */
+int mask_mco_offsets(const float* d_values, int32_t M, int64_t nnz, const void* d_scratch,
+                     const int32_t* d_val_soff, int64_t T, int skip_zero_values,
+                     uint64_t* d_val_mco_mask, int32_t* d_val_mco_off, int64_t* h_nval, void* stream);
+int mask_mco_fill(const int32_t* d_rowptr, const float* d_values, int32_t M, int64_t nnz,
+                  const void* d_scratch, const int32_t* d_val_soff, int64_t T, int skip_zero_values,
+                  const uint64_t* d_val_mco_mask, const int32_t* d_val_mco_off, int64_t nval,
+                  int32_t* d_val_sidx, float* d_val_mco_val, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Row reorders of the Format-DSL host bridge (examples/src_fp32/acc/testbed/custom_format_e2e.cu:
  * 163-347): reverse_cuthill_mckee, first_column_order, jaccard_greedy_order, with the same
@@ -250,6 +268,15 @@ int mask_spmm_metcf(const mask_plan* plan, const int32_t* d_val_soff, const int3
                     const float* d_val_coo_val, int32_t M, int32_t K, int32_t N, const float* d_B,
                     int64_t ldb, float* d_C, int64_t ldc, void* d_scratch, size_t scratch_bytes,
                     int epilogue, void* stream);
+
+/* MCO / BIT-TCF SpMM: same contract; replaces acc_spmm_kernel_tf32tf32fp32
+ * (examples/src_fp32/acc/testbed/kernel.inc:1947) and the bridge's bitmap operators.  The tile operand is expanded from its mask and
+ * compact values in shared memory.  val_mco_mask and val_mco_val must be 16-byte aligned. */
+int mask_spmm_mco(const mask_plan* plan, const int32_t* d_val_soff, const int32_t* d_val_sidx,
+                  const int32_t* d_val_mco_off, const uint64_t* d_val_mco_mask,
+                  const float* d_val_mco_val, int32_t M, int32_t K, int32_t N, const float* d_B,
+                  int64_t ldb, float* d_C, int64_t ldc, void* d_scratch, size_t scratch_bytes,
+                  int epilogue, void* stream);
 
 /* SR-BCRS SpMM for callers that are not allowed to allocate device memory -- a process whose
  * whole device heap belongs to an arena of its own (an inference server, an engine that loads this

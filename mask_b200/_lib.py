@@ -23,6 +23,8 @@ SIGNATURES = {
     "mask_srbcrs_fill": (C.c_int, [vp, vp, vp, i32, i64, vp, vp, i64, vp, vp, vp, vp, vp, vp]),
     "mask_metcf_offsets": (C.c_int, [vp, i32, i64, vp, vp, i64, vp, vp, C.POINTER(i64), vp]),
     "mask_metcf_fill": (C.c_int, [vp, vp, vp, i32, i64, vp, vp, i64, vp, vp, i64, vp, vp, vp, vp]),
+    "mask_mco_offsets": (C.c_int, [vp, i32, i64, vp, vp, i64, C.c_int, vp, vp, C.POINTER(i64), vp]),
+    "mask_mco_fill": (C.c_int, [vp, vp, i32, i64, vp, vp, i64, C.c_int, vp, vp, i64, vp, vp, vp]),
     "mask_reorder_rows": (C.c_int, [C.c_int, vp, vp, i32, i32, vp]),
     "mask_csr_permute_rows": (C.c_int, [vp, vp, vp, i32, vp, vp, vp, vp, vp]),
     "mask_plan_set_row_map": (C.c_int, [vp, vp]),
@@ -46,6 +48,7 @@ SIGNATURES = {
     "mask_plan_status": (C.c_int, [vp, C.POINTER(i32), vp]),
     "mask_spmm_srbcrs": (C.c_int, [vp, vp, vp, vp, i32, i32, i32, vp, i64, vp, i64, vp, sz, C.c_int, vp]),
     "mask_spmm_metcf": (C.c_int, [vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, i64, vp, i64, vp, sz, C.c_int, vp]),
+    "mask_spmm_mco": (C.c_int, [vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, i64, vp, i64, vp, sz, C.c_int, vp]),
     "mask_static_scratch_capacity": (sz, []),
     "mask_spmm_srbcrs_static_scratch": (C.c_int, [vp, vp, vp, vp, i32, i32, i32, vp, i64, vp, i64, C.c_int, vp]),
     "mask_tune": (C.c_int, [C.c_char_p, C.c_int]),

@@ -345,6 +345,46 @@ __global__ void metcf_values_kernel(const int32_t* __restrict__ rowptr, const in
     coo_val[slot] = values ? values[e] : 1.0f;
 }
 
+// MCO (bitmap leaf): bit Swizzle<1,2,3>(8r+c) of the tile's two 64-bit words marks a stored entry.
+__global__ void mco_mask_kernel(const int32_t* __restrict__ row_of, const int32_t* __restrict__ pos,
+                                const float* __restrict__ values, const int32_t* __restrict__ val_soff, int64_t nnz,
+                                int skip_zero_values, unsigned long long* __restrict__ masks) {
+    const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= nnz) return;
+    if (skip_zero_values && values && values[e] == 0.0f) return;
+    const int r = row_of[e], p = pos[e];
+    const int w = r / kWinRows;
+    const int64_t tile = (int64_t)__ldg(val_soff + w) + p / kTileCols;
+    const int phys = sw123((r - w * kWinRows) * kTileCols + p % kTileCols);
+    atomicOr(masks + 2 * tile + (phys >> 6), 1ull << (phys & 63));
+}
+
+struct McoCountIn {
+    const unsigned long long* masks;
+    __device__ int32_t operator()(int64_t t) const { return (__popcll(masks[2 * t]) + __popcll(masks[2 * t + 1]) + 3) & ~3; }
+};
+struct McoOffOut {
+    int32_t* off;
+    __device__ void operator()(int64_t t, int64_t before, int32_t) const { off[t] = (int32_t)before; }
+};
+
+// Values in ascending bit order: an entry's slot is the number of mask bits below its own.
+__global__ void mco_values_kernel(const int32_t* __restrict__ row_of, const int32_t* __restrict__ pos,
+                                  const float* __restrict__ values, const int32_t* __restrict__ val_soff,
+                                  const int32_t* __restrict__ mco_off, const unsigned long long* __restrict__ masks,
+                                  int64_t nnz, int skip_zero_values, float* __restrict__ mco_val) {
+    const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= nnz) return;
+    if (skip_zero_values && values && values[e] == 0.0f) return;
+    const int r = row_of[e], p = pos[e];
+    const int w = r / kWinRows;
+    const int64_t tile = (int64_t)__ldg(val_soff + w) + p / kTileCols;
+    const int phys = sw123((r - w * kWinRows) * kTileCols + p % kTileCols);
+    const unsigned long long m0 = masks[2 * tile], m1 = masks[2 * tile + 1];
+    const int below = phys < 64 ? __popcll(m0 & ((1ull << phys) - 1ull)) : __popcll(m0) + __popcll(m1 & ((1ull << (phys - 64)) - 1ull));
+    mco_val[__ldg(mco_off + tile) + below] = values ? values[e] : 1.0f;
+}
+
 static inline unsigned blocks_for(int64_t n, int threads) { return (unsigned)((n + threads - 1) / threads); }
 
 }  // namespace mask
@@ -477,6 +517,57 @@ extern "C" int mask_metcf_fill(const int32_t* d_rowptr, const int32_t* d_colind,
         metcf_values_kernel<<<blocks_for(nnz, 256), 256, 0, st>>>(d_rowptr, s.row_of, s.pos, d_values, d_val_soff, d_val_coo_off,
                                                                   reinterpret_cast<const unsigned long long*>(d_tile_rows),
                                                                   nnz, d_val_coo_idx, d_val_coo_val);
+        MASK_CUDA_TRY(cudaGetLastError());
+    }
+    return MASK_OK;
+}
+
+extern "C" int mask_mco_offsets(const float* d_values, int32_t M, int64_t nnz, const void* d_scratch, const int32_t* d_val_soff,
+                                int64_t T, int skip_zero_values, uint64_t* d_val_mco_mask, int32_t* d_val_mco_off,
+                                int64_t* h_nval, void* stream) {
+    using namespace mask;
+    MASK_REQUIRE(d_scratch && d_val_soff && d_val_mco_off && h_nval, "NULL argument");
+    MASK_REQUIRE(M >= 1 && nnz >= 0 && T >= 0, "bad sizes");
+    MASK_REQUIRE(T == 0 || d_val_mco_mask, "val_mco_mask is NULL");
+    PackScratch s = carve(const_cast<void*>(d_scratch), M, nnz);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    auto* masks = reinterpret_cast<unsigned long long*>(d_val_mco_mask);
+    if (T > 0) MASK_CUDA_TRY(cudaMemsetAsync(masks, 0, (size_t)T * 16, st));
+    if (nnz > 0) {
+        mco_mask_kernel<<<blocks_for(nnz, 256), 256, 0, st>>>(s.row_of, s.pos, d_values, d_val_soff, nnz, skip_zero_values, masks);
+        MASK_CUDA_TRY(cudaGetLastError());
+    }
+    int rc = device_scan(McoCountIn{masks}, McoOffOut{d_val_mco_off}, T, s.spine, reinterpret_cast<int64_t*>(s.status + 2), st);
+    if (rc != MASK_OK) return rc;
+    int64_t total = 0;
+    MASK_CUDA_TRY(cudaMemcpyAsync(&total, s.status + 2, 8, cudaMemcpyDeviceToHost, st));
+    MASK_CUDA_TRY(cudaStreamSynchronize(st));
+    if (total >= (int64_t)1 << 31) return fail(MASK_ERR_INDEX_OVERFLOW, "value count does not fit int32");
+    const int32_t closing = (int32_t)total;
+    MASK_CUDA_TRY(cudaMemcpyAsync(d_val_mco_off + T, &closing, 4, cudaMemcpyHostToDevice, st));
+    MASK_CUDA_TRY(cudaStreamSynchronize(st));
+    *h_nval = total;
+    return MASK_OK;
+}
+
+extern "C" int mask_mco_fill(const int32_t* d_rowptr, const float* d_values, int32_t M, int64_t nnz, const void* d_scratch,
+                             const int32_t* d_val_soff, int64_t T, int skip_zero_values, const uint64_t* d_val_mco_mask,
+                             const int32_t* d_val_mco_off, int64_t nval, int32_t* d_val_sidx, float* d_val_mco_val,
+                             void* stream) {
+    using namespace mask;
+    MASK_REQUIRE(d_rowptr && d_scratch && d_val_soff && d_val_mco_off, "NULL argument");
+    MASK_REQUIRE(M >= 1 && nnz >= 0 && T >= 0 && nval >= 0, "bad sizes");
+    MASK_REQUIRE(T == 0 || (d_val_sidx && d_val_mco_mask), "output arrays are NULL");
+    MASK_REQUIRE(nval == 0 || d_val_mco_val, "val_mco_val is NULL");
+    PackScratch s = carve(const_cast<void*>(d_scratch), M, nnz);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (nval > 0) MASK_CUDA_TRY(cudaMemsetAsync(d_val_mco_val, 0, (size_t)nval * 4, st));
+    if (nnz > 0) {
+        sidx_kernel<true><<<blocks_for(nnz, 256), 256, 0, st>>>(d_rowptr, s.row_of, s.merged, s.dscan, d_val_soff, M, nnz, d_val_sidx);
+        MASK_CUDA_TRY(cudaGetLastError());
+        mco_values_kernel<<<blocks_for(nnz, 256), 256, 0, st>>>(s.row_of, s.pos, d_values, d_val_soff, d_val_mco_off,
+                                                                reinterpret_cast<const unsigned long long*>(d_val_mco_mask), nnz,
+                                                                skip_zero_values, d_val_mco_val);
         MASK_CUDA_TRY(cudaGetLastError());
     }
     return MASK_OK;

@@ -13,9 +13,10 @@ struct SpmmArgs {
     const int32_t* group_off;
     const int32_t* val_sidx;
     const float* val_blk;      // SR-BCRS
-    const int32_t* coo_off;    // ME-TCF
-    const int32_t* coo_idx;
-    const float* coo_val;
+    const int32_t* coo_off;    // ME-TCF: [begin, end) pairs per tile (+ closing entry); MCO: val_mco_off[T+1]
+    const int32_t* coo_idx;    // ME-TCF
+    const float* coo_val;      // ME-TCF and MCO: the stored values
+    const unsigned long long* mco_mask;   // MCO: two 64-bit words per tile, bit Swizzle<1,2,3>(8r+c)
     float* const* peer_out;    // optional: n_peer_out more output bases (peer GPUs' copies of C, same layout)
     int32_t n_peer_out;
     const int32_t* row_map;    // optional: packed row i is output row row_map[i] (row reorder undone on the fly)
@@ -43,6 +44,25 @@ __device__ __forceinline__ uint32_t rna_bits(float x) { return __float_as_uint(x
 __device__ __forceinline__ float4 ldg_f4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
 
 constexpr int kWarpsPerBlock = 4;
+
+// Tile encodings the kernels read: dense SR-BCRS tiles, ME-TCF COO runs, MCO bitmaps.
+constexpr int kFmtSrbcrs = 0, kFmtMetcf = 1, kFmtMco = 2;
+
+// MCO: the 4 consecutive operand positions 4*lane .. 4*lane+3 of a tile as TF32 operand bits
+// (rounded to nearest, ties away), from the tile's two mask words and its compact values
+// (values in ascending position order): position p holds value number popcount(mask bits below p).
+__device__ __forceinline__ uint4 mco_expand(unsigned long long m0, unsigned long long m1, const uint32_t* vals, int lane) {
+    const unsigned long long m = (lane & 16) ? m1 : m0;
+    const int sh = 4 * (lane & 15);
+    const uint32_t bits = (uint32_t)(m >> sh) & 0xFu;
+    int at = ((lane & 16) ? __popcll(m0) : 0) + __popcll(m & ((1ull << sh) - 1ull));
+    uint4 o = make_uint4(0u, 0u, 0u, 0u);
+    if (bits & 1u) o.x = vals[at++] + 0x1000u;
+    if (bits & 2u) o.y = vals[at++] + 0x1000u;
+    if (bits & 4u) o.z = vals[at++] + 0x1000u;
+    if (bits & 8u) o.w = vals[at] + 0x1000u;
+    return o;
+}
 
 // x + (-0.0f) == x bit for bit for every x (NaN payloads aside); as opaque assembly it yields a
 // fresh register.

@@ -45,10 +45,12 @@ extern int g_session_chunk_cols;      // api.cu: column chunks of the host-buffe
 static int g_tune_umma_variant = 0;   // 0 = slabs by N, 1 / 2 = 128-column slabs with 4 / 2 tiles per step
 static int g_tune_umma = 1;    // 1 = tcgen05 kernel where it applies (see launch_spmm), 2 = whenever N % 128 == 0
 
-template <int NQ, bool METCF, int MIN_BLOCKS>
+template <int NQ, int FMT, int MIN_BLOCKS>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, MIN_BLOCKS) spmm_mma_kernel(const SpmmArgs p) {
-    // ME-TCF: one private 16x8 tile per warp, rebuilt from the tile's COO run.
-    __shared__ __align__(16) float restore[METCF ? kWarpsPerBlock : 1][kTileElems];
+    constexpr bool METCF = FMT == kFmtMetcf, MCO = FMT == kFmtMco;
+    // ME-TCF / MCO: one private 16x8 tile per warp, rebuilt from the tile's COO run or bitmap
+    // (MCO: a second 128-float area stages the tile's compact values).
+    __shared__ __align__(16) float restore[FMT != kFmtSrbcrs ? kWarpsPerBlock * (MCO ? 2 : 1) : 1][kTileElems];
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -66,7 +68,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, MIN_BLOCKS) spmm_mma_kern
 
     // position of this lane's A fragment elements inside a stored tile
     int ao[4];
-    if (METCF) {
+    if (FMT != kFmtSrbcrs) {
         ao[0] = sw123(8 * g + k);       ao[1] = sw123(8 * (g + 8) + k);
         ao[2] = sw123(8 * g + k + 4);   ao[3] = sw123(8 * (g + 8) + k + 4);
     } else {
@@ -93,6 +95,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, MIN_BLOCKS) spmm_mma_kern
     int2 run[2];             // ME-TCF: [begin, end) of the tile's COO run
     int2 ix[2];              // gathered-row ids (k, k+4) of tiles t+2, t+3
     int2 nrun[2];            // ME-TCF: runs of tiles t+2, t+3
+    ulonglong2 mk[2];        // MCO: mask words of the two tiles in flight
+    float4 mv[2];            // MCO: this lane's chunk of the tile's compact values
 
     const float* Bcol = p.B + col_base + 4 * g;
 
@@ -103,6 +107,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, MIN_BLOCKS) spmm_mma_kern
             if (METCF) {
                 nrun[slot].x = __ldg(p.coo_off + 2 * tt);
                 nrun[slot].y = __ldg(p.coo_off + 2 * tt + 1);
+            }
+            if (MCO) {
+                nrun[slot].x = __ldg(p.coo_off + tt);
+                nrun[slot].y = __ldg(p.coo_off + tt + 1);
             }
         }
     };
@@ -129,6 +137,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, MIN_BLOCKS) spmm_mma_kern
                 } else {
                     aidx[buf] = -1;
                 }
+            } else if (MCO) {
+                run[buf] = rn;
+                mk[buf] = __ldg(reinterpret_cast<const ulonglong2*>(p.mco_mask) + tt);
+                if (rn.x + 4 * lane < rn.y) mv[buf] = ldg_f4(p.coo_val + rn.x + 4 * lane);   // runs are multiples of 4 values
             } else {
                 const float* a = p.val_blk + tt * kTileElems;
 #pragma unroll
@@ -201,6 +213,16 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, MIN_BLOCKS) spmm_mma_kern
             __syncwarp();
 #pragma unroll
             for (int i = 0; i < 4; i++) a[i] = rna_bits(tile[ao[i]]);
+        } else if (MCO) {
+            float* tile = restore[2 * warp];
+            float* vals = restore[2 * warp + 1];
+            __syncwarp();
+            if (run[buf].x + 4 * lane < run[buf].y) reinterpret_cast<float4*>(vals)[lane] = mv[buf];
+            __syncwarp();
+            reinterpret_cast<uint4*>(tile)[lane] = mco_expand(mk[buf].x, mk[buf].y, reinterpret_cast<const uint32_t*>(vals), lane);
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 4; i++) a[i] = __float_as_uint(tile[ao[i]]);   // already rounded by mco_expand
         } else {
 #pragma unroll
             for (int i = 0; i < 4; i++) a[i] = rna_bits(areg[buf][i]);
@@ -282,7 +304,7 @@ static int launch_fixup(const mask_plan* plan, const SpmmArgs& a, cudaStream_t s
     return MASK_OK;
 }
 
-template <bool METCF>
+template <int FMT>
 static int launch_spmm(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
     if (plan->G == 0) return MASK_OK;
     a.frag_off = plan->d_frag_off;
@@ -300,6 +322,7 @@ static int launch_spmm(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
     // pipeline step); with 1-2 slabs the mma.sync ring kernel is 10-30 % faster for SR-BCRS, while
     // for ME-TCF it beats the register-pipelined kernel at every width.  umma = 2 forces it.
     const bool umma_fits = N % 128 == 0 && plan->max_group_tiles <= kUmmaMaxGroupTiles;
+    constexpr bool METCF = FMT != kFmtSrbcrs;   // the COO and bitmap leaves take the same routes
     if (umma_fits && (g_tune_umma == 2 || (g_tune_umma == 1 && (METCF || N % 512 == 0)))) {
         int rc = launch_spmm_umma(plan, a, st, g_tune_umma_variant);
         if (rc != MASK_OK) return rc;
@@ -318,14 +341,14 @@ static int launch_spmm(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
     if (grid.y > 65535) return fail(MASK_ERR_INVALID_ARGUMENT, "N too large");
     switch (nq) {
         case 4:
-            if (g_tune_min_blocks == 3) spmm_mma_kernel<4, METCF, 3><<<grid, block, 0, st>>>(a);
-            else spmm_mma_kernel<4, METCF, 2><<<grid, block, 0, st>>>(a);
+            if (g_tune_min_blocks == 3) spmm_mma_kernel<4, FMT, 3><<<grid, block, 0, st>>>(a);
+            else spmm_mma_kernel<4, FMT, 2><<<grid, block, 0, st>>>(a);
             break;
         case 2:
-            if (g_tune_min_blocks == 4) spmm_mma_kernel<2, METCF, 4><<<grid, block, 0, st>>>(a);
-            else spmm_mma_kernel<2, METCF, 3><<<grid, block, 0, st>>>(a);
+            if (g_tune_min_blocks == 4) spmm_mma_kernel<2, FMT, 4><<<grid, block, 0, st>>>(a);
+            else spmm_mma_kernel<2, FMT, 3><<<grid, block, 0, st>>>(a);
             break;
-        default: spmm_mma_kernel<1, METCF, 4><<<grid, block, 0, st>>>(a); break;
+        default: spmm_mma_kernel<1, FMT, 4><<<grid, block, 0, st>>>(a); break;
     }
     MASK_CUDA_TRY(cudaGetLastError());
     return launch_fixup(plan, a, st);
@@ -383,7 +406,7 @@ extern "C" int mask_spmm_srbcrs(const mask_plan* plan, const int32_t* d_val_soff
     a.B = d_B; a.ldb = ldb; a.C = d_C; a.ldc = ldc;
     a.scratch = static_cast<float*>(d_scratch);
     a.M = M; a.N = N; a.relu = (epilogue == MASK_EPILOGUE_RELU);
-    return launch_spmm<false>(plan, a, static_cast<cudaStream_t>(stream));
+    return launch_spmm<kFmtSrbcrs>(plan, a, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int mask_spmm_metcf(const mask_plan* plan, const int32_t* d_val_soff, const int32_t* d_val_sidx,
@@ -402,5 +425,28 @@ extern "C" int mask_spmm_metcf(const mask_plan* plan, const int32_t* d_val_soff,
     a.B = d_B; a.ldb = ldb; a.C = d_C; a.ldc = ldc;
     a.scratch = static_cast<float*>(d_scratch);
     a.M = M; a.N = N; a.relu = (epilogue == MASK_EPILOGUE_RELU);
-    return launch_spmm<true>(plan, a, static_cast<cudaStream_t>(stream));
+    return launch_spmm<kFmtMetcf>(plan, a, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mask_spmm_mco(const mask_plan* plan, const int32_t* d_val_soff, const int32_t* d_val_sidx,
+                             const int32_t* d_val_mco_off, const uint64_t* d_val_mco_mask, const float* d_val_mco_val,
+                             int32_t M, int32_t K, int32_t N, const float* d_B, int64_t ldb, float* d_C, int64_t ldc,
+                             void* d_scratch, size_t scratch_bytes, int epilogue, void* stream) {
+    using namespace mask;
+    (void)d_val_soff;
+    int rc = check_common(plan, M, K, N, d_B, ldb, d_C, ldc, d_scratch, scratch_bytes);
+    if (rc != MASK_OK || N == 0) return rc;
+    MASK_REQUIRE(plan->T == 0 || (d_val_sidx != nullptr && d_val_mco_off != nullptr && d_val_mco_mask != nullptr),
+                 "packed arrays are NULL");
+    MASK_REQUIRE((reinterpret_cast<uintptr_t>(d_val_mco_mask) & 15) == 0 && (reinterpret_cast<uintptr_t>(d_val_mco_val) & 15) == 0,
+                 "val_mco_mask and val_mco_val must be 16-byte aligned");
+    SpmmArgs a{};
+    a.val_sidx = d_val_sidx;
+    a.coo_off = d_val_mco_off;
+    a.coo_val = d_val_mco_val;
+    a.mco_mask = reinterpret_cast<const unsigned long long*>(d_val_mco_mask);
+    a.B = d_B; a.ldb = ldb; a.C = d_C; a.ldc = ldc;
+    a.scratch = static_cast<float*>(d_scratch);
+    a.M = M; a.N = N; a.relu = (epilogue == MASK_EPILOGUE_RELU);
+    return launch_spmm<kFmtMco>(plan, a, static_cast<cudaStream_t>(stream));
 }

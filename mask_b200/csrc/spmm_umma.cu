@@ -56,8 +56,10 @@ constexpr long long kUmmaWaitCycles = 2000000000LL;
 //            matrix is swept once per slab, so rows of B compete for L2 with 512 bytes each instead
 //            of 4N bytes -- the lever against re-reading B on power-law matrices).
 // Either way a stage is one pipeline step: one full/ready/empty round trip and U MMAs.
-template <int NSLAB, int KB, int S>
+template <int NSLAB, int KB, int S, int FMT = kFmtSrbcrs>
 struct UmmaLayout {
+    // staging per stage and tile: ME-TCF 32 idx + 32 val of the run; MCO 16 B of mask + up to 128 values
+    static constexpr int kCooStride = FMT == kFmtMco ? 528 : 256;
     static constexpr int kUnits = NSLAB * KB;
     static constexpr int kTilesPerStep = KB;
     static constexpr int kBBytes = kUnits * 4096;                 // gathered rows of one step
@@ -67,8 +69,10 @@ struct UmmaLayout {
     static constexpr int kA = S * kBBytes;
     static constexpr int kIds = kA + S * kABytes;
     static constexpr int kRuns = kIds + kUmmaIdsBytes;            // ME-TCF: [begin, end) of every tile's COO run
-    static constexpr int kCoo = kRuns + kUmmaMaxGroupTiles * 8;   // ME-TCF: per stage and tile 32 idx + 32 val of the run
-    static constexpr int kBars = kCoo + S * KB * 256;             // full[S], empty[S], ready[S], acc_full[2], acc_empty[2]
+    // ME-TCF: [begin, end) per tile; MCO: val_mco_off of the group's tiles plus the closing entry
+    static constexpr int kRunsBytes = FMT == kFmtMco ? ((kUmmaMaxGroupTiles + 1) * 4 + 15) & ~15 : kUmmaMaxGroupTiles * 8;
+    static constexpr int kCoo = kRuns + kRunsBytes;
+    static constexpr int kBars = kCoo + ((S * KB * kCooStride + 15) & ~15);   // full[S], empty[S], ready[S], acc_full[2], acc_empty[2]
     static constexpr int kTmemSlot = kBars + (3 * S + 4) * 8;
     static constexpr int kAbort = kTmemSlot + 8;
     static constexpr int kBytes = kAbort + 8;
@@ -143,10 +147,13 @@ __device__ __forceinline__ void cp16(uint32_t dst, const void* src) {
 // kernel.inc:822-840 does the same in its shared-memory restore step).  ME-TCF's index
 // Swizzle<1,2,3>(8r+c) is exactly the K-major SWIZZLE_32B operand layout, so tile[idx] = value
 // yields the operand directly, rows unpermuted.
-template <int NSLAB, int KB, int S, int MIN_BLOCKS, bool METCF>
+// MCO: the operand is expanded from the tile's 128-bit mask and its compact values (bit and operand
+// position are both Swizzle<1,2,3>(8r+c)): no zero-fill, no scatter, one 16-byte store per lane.
+template <int NSLAB, int KB, int S, int MIN_BLOCKS, int FMT>
 __global__ void __launch_bounds__(kUmmaThreads, MIN_BLOCKS) spmm_umma_kernel(const SpmmArgs p, int32_t* status) {
     static_assert(KB == 1 || NSLAB == 1, "tiles are batched along K only in single-slab blocks");
-    using L = UmmaLayout<NSLAB, KB, S>;
+    constexpr bool METCF = FMT == kFmtMetcf, MCO = FMT == kFmtMco;
+    using L = UmmaLayout<NSLAB, KB, S, FMT>;
     constexpr int kAccCols = 16 * NSLAB;                          // accumulator columns per buffer
     extern __shared__ unsigned char umma_smem_raw[];
     const uint32_t raw = (uint32_t)__cvta_generic_to_shared(umma_smem_raw);
@@ -193,6 +200,10 @@ __global__ void __launch_bounds__(kUmmaThreads, MIN_BLOCKS) spmm_umma_kernel(con
         if (METCF) {  // run offsets coo_off[2t], coo_off[2t+1]: 8-byte aligned pairs
             for (int c = pt; c < n_tiles; c += 128)
                 asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(base + L::kRuns + c * 8), "l"(p.coo_off + 2 * (int64_t)(t0 + c)) : "memory");
+        }
+        if (MCO) {    // value offsets val_mco_off[t0 .. t0 + n_tiles]
+            for (int c = pt; c <= n_tiles; c += 128)
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(base + L::kRuns + c * 4), "l"(p.coo_off + (int64_t)(t0 + c)) : "memory");
         }
         asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
     }
@@ -245,6 +256,12 @@ __global__ void __launch_bounds__(kUmmaThreads, MIN_BLOCKS) spmm_umma_kernel(con
                                                        : static_cast<const void*>(p.coo_val + run.x + 4 * chunk);
                             cp16(base + L::kCoo + (s * KB + pw) * 256 + lane * 16, src);
                         }
+                    } else if (MCO) {
+                        const int* offs = reinterpret_cast<const int*>(gbase + L::kRuns);
+                        const int o0 = offs[tile], o1 = offs[tile + 1];
+                        const uint32_t st = base + L::kCoo + (s * KB + pw) * L::kCooStride;
+                        if (lane == 0) cp16(st, p.mco_mask + 2 * (int64_t)(t0 + tile));
+                        if (o0 + 4 * lane < o1) cp16(st + 16 + lane * 16, p.coo_val + o0 + 4 * lane);   // runs are multiples of 4 values
                     } else {
                         cp16(base + L::kA + s * L::kABytes + pw * kUmmaABytes + lane * 16,
                              p.val_blk + (int64_t)(t0 + tile) * kTileElems + lane * 4);
@@ -283,6 +300,10 @@ __global__ void __launch_bounds__(kUmmaThreads, MIN_BLOCKS) spmm_umma_kernel(con
                             for (int e = run.x + 32 + lane; e < run.y; e += 32)   // dense tiles: entries beyond the staged 32
                                 tile[__ldg(p.coo_idx + e)] = __float_as_uint(__ldg(p.coo_val + e)) + 0x1000u;
                             __syncwarp();
+                        } else if (MCO) {
+                            const unsigned char* st = gbase + L::kCoo + (s * KB + u) * L::kCooStride;
+                            const ulonglong2 m = *reinterpret_cast<const ulonglong2*>(st);
+                            reinterpret_cast<uint4*>(aslot)[lane] = mco_expand(m.x, m.y, reinterpret_cast<const uint32_t*>(st + 16), lane);
                         } else if (!(p.hints & 4)) {  // round the tile values to TF32 (nearest, ties away) in place
                             uint4* at = reinterpret_cast<uint4*>(aslot) + lane;
                             uint4 v = *at;
@@ -382,7 +403,7 @@ __global__ void __launch_bounds__(kUmmaThreads, MIN_BLOCKS) spmm_umma_kernel(con
                 asm volatile("" : "+r"(row0));   // keeps the 16 row offsets from being hoisted out of this loop into registers
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
-                    const int r = METCF ? i : (i ^ (i >> 3));   // MMA-N index -> window row (SR-BCRS: rows 8..15 swapped pairwise)
+                    const int r = FMT != kFmtSrbcrs ? i : (i ^ (i >> 3));   // MMA-N index -> window row (SR-BCRS: rows 8..15 swapped pairwise)
                     if (r < rows_ok) {
                         const int64_t off = slot >= 0 ? (int64_t)r * p.N
                                                       : (int64_t)(p.row_map ? p.row_map[row0 + r] : row0 + r) * p.ldc;
@@ -406,12 +427,16 @@ __global__ void __launch_bounds__(kUmmaThreads, MIN_BLOCKS) spmm_umma_kernel(con
 
 template <int NSLAB, int KB, int S, int MIN_BLOCKS>
 static int launch_umma_variant(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st) {
-    using L = UmmaLayout<NSLAB, KB, S>;
-    auto kern = a.coo_off ? spmm_umma_kernel<NSLAB, KB, S, MIN_BLOCKS, true> : spmm_umma_kernel<NSLAB, KB, S, MIN_BLOCKS, false>;
-    MASK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));
+    const int fmt = a.mco_mask ? kFmtMco : (a.coo_off ? kFmtMetcf : kFmtSrbcrs);
+    auto kern = fmt == kFmtMco ? spmm_umma_kernel<NSLAB, KB, S, MIN_BLOCKS, kFmtMco>
+                               : (fmt == kFmtMetcf ? spmm_umma_kernel<NSLAB, KB, S, MIN_BLOCKS, kFmtMetcf>
+                                                   : spmm_umma_kernel<NSLAB, KB, S, MIN_BLOCKS, kFmtSrbcrs>);
+    const int smem = fmt == kFmtMco ? UmmaLayout<NSLAB, KB, S, kFmtMco>::kDynamicBytes : UmmaLayout<NSLAB, KB, S>::kDynamicBytes;
+    static_assert(MIN_BLOCKS * (UmmaLayout<NSLAB, KB, S, kFmtMco>::kDynamicBytes + 1024) <= 228 * 1024, "shared memory per SM");
+    MASK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     dim3 grid((unsigned)plan->G, (unsigned)(a.N / (NSLAB * 128)));
     if (grid.y > 65535) return fail(MASK_ERR_INVALID_ARGUMENT, "N too large");
-    kern<<<grid, kUmmaThreads, L::kDynamicBytes, st>>>(a, plan->d_status);
+    kern<<<grid, kUmmaThreads, smem, st>>>(a, plan->d_status);
     MASK_CUDA_TRY(cudaGetLastError());
     return MASK_OK;
 }

@@ -145,6 +145,27 @@ class PackedMETCF:
     new_plan = PackedSRBCRS.new_plan
 
 
+@dataclass
+class PackedMCO:
+    """MCO / BIT-TCF: val_soff, val_sidx (tail = last real column), val_mco_off int32[T+1],
+    val_mco_mask int64[2T] (bit Swizzle<1,2,3>(8r+c)), val_mco_val float32[nval]."""
+    M: int
+    K: int
+    T: int
+    nnz: int
+    nval: int
+    val_soff: torch.Tensor
+    val_sidx: torch.Tensor
+    val_mco_off: torch.Tensor
+    val_mco_mask: torch.Tensor
+    val_mco_val: torch.Tensor
+    row_order: torch.Tensor | None = None
+    plans: dict = field(default_factory=dict)
+
+    plan = PackedSRBCRS.plan
+    new_plan = PackedSRBCRS.new_plan
+
+
 def _analyze(rowptr, colind, M, K):
     _req(rowptr, torch.int32, "rowptr")
     _req(colind, torch.int32, "colind")
@@ -236,6 +257,28 @@ def pack_metcf(rowptr, colind, values, M: int, K: int) -> PackedMETCF:
     return PackedMETCF(M, K, T, nnz, nnz_pad, val_soff, val_sidx, val_coo_off, val_coo_idx, val_coo_val)
 
 
+def pack_mco(rowptr, colind, values, M: int, K: int, skip_zero_values: bool = False) -> PackedMCO:
+    """CSR (device) -> MCO / BIT-TCF on the device.  ``skip_zero_values`` follows the Format-DSL
+    bridge (explicit zeros are dropped); the BIT-TCF testbed keeps them."""
+    if values is not None:
+        _req(values, torch.float32, "values")
+    ws, val_soff, T, nnz = _analyze(rowptr, colind, M, K)
+    dev = rowptr.device
+    L = lib()
+    val_mco_mask = torch.empty(2 * max(T, 1), dtype=torch.int64, device=dev)
+    val_mco_off = torch.empty(T + 1, dtype=torch.int32, device=dev)
+    nv = C.c_int64(0)
+    check(L.mask_mco_offsets(_ptr(values), M, nnz, _ptr(ws), _ptr(val_soff), T, int(skip_zero_values), _ptr(val_mco_mask),
+                             _ptr(val_mco_off), C.byref(nv), _stream()), "mask_mco_offsets")
+    nval = int(nv.value)
+    val_sidx = torch.empty(8 * T, dtype=torch.int32, device=dev)
+    val_mco_val = torch.empty(max(nval, 4), dtype=torch.float32, device=dev)
+    check(L.mask_mco_fill(_ptr(rowptr), _ptr(values), M, nnz, _ptr(ws), _ptr(val_soff), T, int(skip_zero_values),
+                          _ptr(val_mco_mask), _ptr(val_mco_off), nval, _ptr(val_sidx), _ptr(val_mco_val), _stream()),
+          "mask_mco_fill")
+    return PackedMCO(M, K, T, nnz, nval, val_soff, val_sidx, val_mco_off, val_mco_mask[:2 * T], val_mco_val[:nval])
+
+
 def spmm(packed, dense: torch.Tensor, out: torch.Tensor | None = None, policy: str = "auto", relu: bool = False,
          plan: Plan | None = None) -> torch.Tensor:
     """out[M,N] = A @ dense[K,N] on the current stream.  ``out`` is fully overwritten."""
@@ -260,7 +303,11 @@ def spmm(packed, dense: torch.Tensor, out: torch.Tensor | None = None, policy: s
     sb = 0 if scratch is None else scratch.numel()
     epi = _lib.EPILOGUE_RELU if relu else _lib.EPILOGUE_NONE
     L = lib()
-    if isinstance(packed, PackedMETCF):
+    if isinstance(packed, PackedMCO):
+        check(L.mask_spmm_mco(plan._h, _ptr(packed.val_soff), _ptr(packed.val_sidx), _ptr(packed.val_mco_off),
+                              _ptr(packed.val_mco_mask), _ptr(packed.val_mco_val), packed.M, packed.K, N, _ptr(dense),
+                              N, _ptr(out), N, _ptr(scratch), sb, epi, _stream()), "mask_spmm_mco")
+    elif isinstance(packed, PackedMETCF):
         check(L.mask_spmm_metcf(plan._h, _ptr(packed.val_soff), _ptr(packed.val_sidx), _ptr(packed.val_coo_off),
                                 _ptr(packed.val_coo_idx), _ptr(packed.val_coo_val), packed.M, packed.K, N, _ptr(dense),
                                 N, _ptr(out), N, _ptr(scratch), sb, epi, _stream()), "mask_spmm_metcf")

@@ -132,6 +132,38 @@ def pack_metcf(M, rowptr, colind, values):
                 nnz_pad=pad)
 
 
+def pack_mco(M, rowptr, colind, values, skip_zero_values=False):
+    """-> dict(val_soff, val_sidx, val_mco_off int32[T+1], val_mco_mask uint64[2T], val_mco_val f32[nval], T, nval)."""
+    L = lib()
+    rowptr, colind, values = _c(rowptr, np.int32), _c(colind, np.int32), _c(values, np.float32)
+    W = (M + 15) // 16
+    soff = np.zeros(W + 1, dtype=np.int32)
+    T = int(L.oracle_srbcrs_count(M, rowptr, colind, soff))
+    sidx = np.zeros(8 * T, dtype=np.int32)
+    off = np.zeros(T + 1, dtype=np.int32)
+    mask = np.zeros(2 * T, dtype=np.uint64)
+    val = np.zeros(len(values) + 3 * T + 4, dtype=np.float32)
+    L.oracle_mco_pack.restype = C.c_int64
+    L.oracle_mco_pack.argtypes = [C.c_int] + [C.c_void_p] * 3 + [C.c_int] + [C.c_void_p] * 5
+    nval = int(L.oracle_mco_pack(M, rowptr.ctypes.data, colind.ctypes.data, values.ctypes.data, int(skip_zero_values),
+                                 soff.ctypes.data, sidx.ctypes.data, off.ctypes.data, mask.ctypes.data, val.ctypes.data))
+    return dict(val_soff=soff, val_sidx=sidx, val_mco_off=off, val_mco_mask=mask, val_mco_val=val[:nval].copy(), T=T, nval=nval)
+
+
+def spmm_from_mco(M, packed, B, round_tf32=False):
+    L = lib()
+    B = _c(B, np.float32)
+    N = B.shape[1]
+    out = np.empty((M, N), dtype=np.float32)
+    L.oracle_spmm_from_mco.restype = None
+    L.oracle_spmm_from_mco.argtypes = [C.c_int, C.c_int] + [C.c_void_p] * 6 + [C.c_int64, C.c_void_p, C.c_int64, C.c_int]
+    a = {k: np.ascontiguousarray(packed[k]) for k in ("val_soff", "val_sidx", "val_mco_off", "val_mco_mask", "val_mco_val")}
+    L.oracle_spmm_from_mco(M, N, a["val_soff"].ctypes.data, a["val_sidx"].ctypes.data, a["val_mco_off"].ctypes.data,
+                           a["val_mco_mask"].ctypes.data, a["val_mco_val"].ctypes.data, B.ctypes.data, N, out.ctypes.data, N,
+                           int(round_tf32))
+    return out
+
+
 def strict_lb_plan(M, val_soff, workload=64):
     """-> (row_block_offset int32[F+1], row_block_to_window int32[F], group_offset int32[G+1])."""
     L = lib()
@@ -199,6 +231,31 @@ def ref_reorder_rows(kind, M, K, rowptr, colind):
     if rc != 0:
         raise ValueError(f"reference reorder failed ({rc})")
     return order
+
+
+def ref_pack_mco(M, K, rowptr, colind, values):
+    """The Format-DSL bridge's own packer in its bitmap ("column_condensed") mode, built from the
+    reference sources: dict like pack_mco(skip_zero_values=True); the bridge pads the value array
+    to a multiple of 8 at the very end, which is cut off here."""
+    R = _ref("libref_bridge_mco.so")
+    R.ref_bridge_pack.restype = C.c_int
+    R.ref_bridge_pack.argtypes = [C.c_int, C.c_int] + [C.c_void_p] * 10
+    rowptr, colind, values = _c(rowptr, np.int32), _c(colind, np.int32), _c(values, np.float32)
+    tiles, nv = C.c_int(0), C.c_longlong(0)
+    args = (M, K, rowptr.ctypes.data, colind.ctypes.data, values.ctypes.data, C.addressof(tiles), C.addressof(nv))
+    if R.ref_bridge_pack(*args, None, None, None, None, None) != 0:
+        raise ValueError("reference bridge packer failed")
+    T, n = tiles.value, nv.value
+    W = (M + 15) // 16
+    soff = np.zeros(W + 1, dtype=np.int32)
+    sidx = np.zeros(8 * T, dtype=np.int32)
+    off = np.zeros(T + 1, dtype=np.int32)
+    mask = np.zeros(2 * T, dtype=np.uint64)
+    val = np.zeros(max(n, 1), dtype=np.float32)
+    if R.ref_bridge_pack(*args, soff.ctypes.data, sidx.ctypes.data, off.ctypes.data, mask.ctypes.data, val.ctypes.data) != 0:
+        raise ValueError("reference bridge packer failed")
+    nval = int(off[T])
+    return dict(val_soff=soff, val_sidx=sidx, val_mco_off=off, val_mco_mask=mask, val_mco_val=val[:nval].copy(), T=T, nval=nval)
 
 
 def max_threads() -> int:
@@ -269,7 +326,7 @@ def check_tolerance(got, ref, absprod, rtol=RTOL, atol=ATOL):
 def ref_available() -> bool:
     return all(os.path.exists(os.path.join(_HERE, "_ref", n)) for n in
                ("libref_srbcrs.so", "libref_strict_lb.so", "libref_multi_bind.so", "libref_metcf.so",
-                "libref_bridge.so"))
+                "libref_bridge.so", "libref_bridge_mco.so"))
 
 
 def _ref(name):

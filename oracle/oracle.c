@@ -231,6 +231,65 @@ void oracle_metcf_fill(int M, const int* rowptr, const int* colind, const float*
     free(cur);
 }
 
+/* ---- MCO / BIT-TCF (bitmap leaf) -----------------------------------------------------------
+ * examples/src_fp32/acc/testbed/main.cu:300-383 (BIT-TCF testbed) and the Format-DSL bridge's
+ * column_condensed mode (examples/src_fp32/acc/testbed/custom_format_e2e.cu:527-552): tiling and
+ * val_sidx as SR-BCRS (tail = the window's last real column); per tile two 64-bit words with bit
+ * Swizzle<1,2,3>(8r+c) set for every stored entry (LSB first, main.cu:96-118), the values in
+ * ascending bit order padded with zeros to a multiple of 4, val_mco_off[t] = start of tile t's
+ * values.  skip_zero_values = 1 is the bridge (entries equal to 0.0f are dropped, :543), 0 the
+ * testbed.  val_soff comes from oracle_srbcrs_count; mco_val needs room for nnz + 3T floats.
+ * Returns the number of stored values (val_mco_off[T]). */
+int64_t oracle_mco_pack(int M, const int* rowptr, const int* colind, const float* values,
+                        int skip_zero_values, const int* val_soff, int* val_sidx, int* val_mco_off,
+                        uint64_t* val_mco_mask, float* val_mco_val) {
+    int W = (M + WIN_ROWS - 1) / WIN_ROWS;
+    int cap = max_window_nnz(M, rowptr);
+    int* U = (int*)malloc(sizeof(int) * (size_t)(cap > 0 ? cap : 1));
+    int max_nt = 1;
+    for (int w = 0; w < W; w++)
+        if (val_soff[w + 1] - val_soff[w] > max_nt) max_nt = val_soff[w + 1] - val_soff[w];
+    float* tv = (float*)malloc(sizeof(float) * (size_t)max_nt * TILE_ELEMS);
+    unsigned char* present = (unsigned char*)malloc((size_t)max_nt * TILE_ELEMS);
+    int64_t pos = 0;
+    for (int w = 0; w < W; w++) {
+        int u = window_unique_cols(M, rowptr, colind, w, U);
+        int nt = val_soff[w + 1] - val_soff[w];
+        int* sidx = val_sidx + (int64_t)val_soff[w] * TILE_COLS;
+        for (int i = 0; i < nt * TILE_COLS; i++) sidx[i] = U[i < u ? i : u - 1];
+        memset(present, 0, (size_t)nt * TILE_ELEMS);
+        int r0 = w * WIN_ROWS, r1 = r0 + WIN_ROWS;
+        if (r1 > M) r1 = M;
+        for (int row = r0; row < r1; row++) {
+            for (int e = rowptr[row]; e < rowptr[row + 1]; e++) {
+                if (skip_zero_values && values[e] == 0.0f) continue;
+                int p = lower_bound_int(U, u, colind[e]);
+                int at = (p / TILE_COLS) * TILE_ELEMS + sw123((row - r0) * TILE_COLS + p % TILE_COLS);
+                present[at] = 1;
+                tv[at] = values[e];
+            }
+        }
+        for (int b = 0; b < nt; b++) {
+            int t = val_soff[w] + b;
+            uint64_t m0 = 0, m1 = 0;
+            val_mco_off[t] = (int)pos;
+            for (int i = 0; i < TILE_ELEMS; i++) {
+                if (!present[b * TILE_ELEMS + i]) continue;
+                if (i < 64) m0 |= (uint64_t)1 << i; else m1 |= (uint64_t)1 << (i - 64);
+                val_mco_val[pos++] = tv[b * TILE_ELEMS + i];
+            }
+            while (pos % 4 != 0) val_mco_val[pos++] = 0.0f;
+            val_mco_mask[2 * (int64_t)t] = m0;
+            val_mco_mask[2 * (int64_t)t + 1] = m1;
+        }
+    }
+    val_mco_off[val_soff[W]] = (int)pos;
+    free(U);
+    free(tv);
+    free(present);
+    return pos;
+}
+
 /* ---- task planners -----------------------------------------------------------------------
  * Strict load balance (examples/src_fp32/sr_bcrs/testbed/main_strict_lb_16x8.cu:208-256):
  * walk windows in order, cut their tile ranges into fragments so that every group of
@@ -415,6 +474,42 @@ void oracle_spmm_from_metcf(int M, int N, const int* val_soff, const int* val_si
             memset(tile, 0, sizeof(tile));
             for (int p = val_coo_off[2 * t]; p < val_coo_off[2 * t + 1]; p++)
                 tile[val_coo_idx[p]] = val_coo_val[p];
+            for (int r = 0; r < rows; r++) {
+                float* c = C + (int64_t)(w * WIN_ROWS + r) * ldc;
+                for (int k = 0; k < TILE_COLS; k++) {
+                    float a = tile[sw123(r * TILE_COLS + k)];
+                    if (a == 0.0f) continue;
+                    if (round_tf32) a = rna_tf32(a);
+                    const float* b = B + (int64_t)val_sidx[(int64_t)t * TILE_COLS + k] * ldb;
+                    if (round_tf32) for (int n = 0; n < N; n++) c[n] += a * rna_tf32(b[n]);
+                    else for (int n = 0; n < N; n++) c[n] += a * b[n];
+                }
+            }
+        }
+    }
+}
+
+/* The product from MCO arrays: tile element (r, k) is stored iff bit Swizzle<1,2,3>(8r+k) is set;
+ * its value is number popcount(bits below) of the tile's run. */
+void oracle_spmm_from_mco(int M, int N, const int* val_soff, const int* val_sidx, const int* val_mco_off,
+                          const uint64_t* val_mco_mask, const float* val_mco_val, const float* B, int64_t ldb,
+                          float* C, int64_t ldc, int round_tf32) {
+    int W = (M + WIN_ROWS - 1) / WIN_ROWS;
+#pragma omp parallel for schedule(dynamic, 16)
+    for (int w = 0; w < W; w++) {
+        float tile[TILE_ELEMS];
+        int rows = M - w * WIN_ROWS;
+        if (rows > WIN_ROWS) rows = WIN_ROWS;
+        for (int r = 0; r < rows; r++) {
+            float* c = C + (int64_t)(w * WIN_ROWS + r) * ldc;
+            for (int n = 0; n < N; n++) c[n] = 0.0f;
+        }
+        for (int t = val_soff[w]; t < val_soff[w + 1]; t++) {
+            int at = val_mco_off[t];
+            for (int i = 0; i < TILE_ELEMS; i++) {
+                uint64_t word = val_mco_mask[2 * (int64_t)t + (i >> 6)];
+                tile[i] = ((word >> (i & 63)) & 1) ? val_mco_val[at++] : 0.0f;
+            }
             for (int r = 0; r < rows; r++) {
                 float* c = C + (int64_t)(w * WIN_ROWS + r) * ldc;
                 for (int k = 0; k < TILE_COLS; k++) {

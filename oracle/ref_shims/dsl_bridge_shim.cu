@@ -30,3 +30,25 @@ int ref_reorder_rows(int kind, int m, int k, const int* row_ptr, const int* col_
 }
 
 }  // extern "C"
+
+// The bridge's own packer (convert_to_mco, custom_format_e2e.cu:478-800) for whatever packing mode
+// this shim was compiled with: mode 0 ("column_condensed") yields the MCO bitmap leaf.  Two-call
+// protocol: with NULL arrays only the sizes are returned.
+extern "C" int ref_bridge_pack(int m, int k, const int* row_ptr, const int* col_idx, const float* vals, int* tiles,
+                               long long* n_values, int* row_offsets, int* sparse_columns, int* value_offsets,
+                               unsigned long long* masks, float* values) {
+    try {
+        const sparsene_custom_e2e::PackedMco p =
+            sparsene_custom_e2e::convert_to_mco(m, k, row_ptr, col_idx, vals, 32, "row", 64);
+        *tiles = p.tiles;
+        *n_values = (long long)p.values.size();
+        if (row_offsets) std::memcpy(row_offsets, p.row_offsets.data(), sizeof(int) * p.row_offsets.size());
+        if (sparse_columns) std::memcpy(sparse_columns, p.sparse_columns.data(), sizeof(int) * p.sparse_columns.size());
+        if (value_offsets) std::memcpy(value_offsets, p.value_offsets.data(), sizeof(int) * p.value_offsets.size());
+        if (masks && !p.masks.empty()) std::memcpy(masks, p.masks.data(), sizeof(uint64_t) * p.masks.size());
+        if (values && !p.values.empty()) std::memcpy(values, p.values.data(), sizeof(float) * p.values.size());
+    } catch (const std::exception&) {
+        return 2;
+    }
+    return 0;
+}

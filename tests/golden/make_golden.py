@@ -64,6 +64,9 @@ def main():
                    sr_val_soff=sr["val_soff"], sr_val_sidx=sr["val_sidx"], sr_val_block_val=sr["val_block_val"],
                    me_val_soff=me["val_soff"], me_val_sidx=me["val_sidx"], me_val_coo_off=me["val_coo_off"],
                    me_val_coo_idx=me["val_coo_idx"], me_val_coo_val=me["val_coo_val"])
+        mc = oracle.ref_pack_mco(m.M, m.K, m.rowptr, m.colind, m.values)
+        out.update(mco_val_soff=mc["val_soff"], mco_val_sidx=mc["val_sidx"], mco_val_mco_off=mc["val_mco_off"],
+                   mco_val_mco_mask=mc["val_mco_mask"], mco_val_mco_val=mc["val_mco_val"])
         for wl in (64, 8):
             rbo, rb2w, go = oracle.ref_strict_lb_plan(m.M, sr["val_soff"], wl)
             out[f"slb{wl}_row_block_offset"] = rbo

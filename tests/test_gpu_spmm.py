@@ -136,6 +136,43 @@ def test_metcf_spmm_matches_oracle(oracle_mod, name, N):
     _assert_close(oracle_mod, m, B, out3.cpu().numpy())
 
 
+@pytest.mark.parametrize("name", ["m1", "m17", "m33_empty_window", "hub_rows", "rmat10", "stencil8", "all_empty",
+                                  "one_tile_windows", "uniform512"])
+@pytest.mark.parametrize("N", [40, 128, 256, 512])
+def test_mco_spmm_matches_oracle(oracle_mod, name, N):
+    """MCO / BIT-TCF (bitmap leaf): tcgen05 kernel for N % 128 == 0 in every slab variant, the
+    register-pipelined kernel otherwise, split windows, ReLU; and exactly the product the oracle
+    computes from the same arrays with both operands rounded."""
+    import torch
+    from mask_b200 import engine
+    m = cases.SMALL[name]()
+    rp, ci, va = _dev(m)
+    p = engine.pack_mco(rp, ci, va, m.M, m.K)
+    B = _dense(m.K, N, 29)
+    Bd = torch.from_numpy(B).cuda()
+    out = torch.full((m.M, N), float("nan"), device="cuda")
+    engine.spmm(p, Bd, out=out)
+    _assert_close(oracle_mod, m, B, out.cpu().numpy())
+    plan2 = engine.Plan(p.val_soff, m.M, p.T, "auto", 2)
+    out2 = engine.spmm(p, Bd, plan=plan2, relu=True)
+    _assert_close(oracle_mod, m, B, out2.cpu().numpy(), relu=True)
+    assert plan2.status() == 0
+    outs = []
+    try:
+        for umma, variant in ((0, 0), (2, 1), (2, 3)):
+            engine.tune("umma", umma)
+            engine.tune("umma_variant", variant)
+            o = torch.full((m.M, N), float("nan"), device="cuda")
+            engine.spmm(p, Bd, out=o, plan=plan2)
+            outs.append(o)
+    finally:
+        engine.tune("umma", 1)
+        engine.tune("umma_variant", 0)
+    for o in outs:
+        _assert_close(oracle_mod, m, B, o.cpu().numpy())
+    assert plan2.status() == 0
+
+
 def test_relu_epilogue(oracle_mod):
     import torch
     from mask_b200 import engine

@@ -18,6 +18,9 @@ def test_oracle_matches_golden(oracle_mod, name):
     me = oracle_mod.pack_metcf(m.M, m.rowptr, m.colind, m.values)
     for k in ("val_soff", "val_sidx", "val_coo_off", "val_coo_idx", "val_coo_val"):
         assert np.array_equal(BITS(me[k]), BITS(g["me_" + k])), (name, k)
+    mc = oracle_mod.pack_mco(m.M, m.rowptr, m.colind, m.values, skip_zero_values=True)
+    for k in ("val_soff", "val_sidx", "val_mco_off", "val_mco_mask", "val_mco_val"):
+        assert np.array_equal(BITS(mc[k]), BITS(g["mco_" + k])), (name, k)
     for wl in (64, 8):
         rbo, rb2w, go = oracle_mod.strict_lb_plan(m.M, sr["val_soff"], wl)
         assert np.array_equal(rbo, g[f"slb{wl}_row_block_offset"])
@@ -44,6 +47,11 @@ def test_oracle_matches_reference_build(oracle_mod, name):
     assert me["T"] == rm["T"] and me["nnz_pad"] == rm["nnz_pad"]
     for k in ("val_soff", "val_sidx", "val_coo_off", "val_coo_idx", "val_coo_val"):
         assert np.array_equal(BITS(me[k]), BITS(rm[k])), (name, k)
+    mc = oracle_mod.pack_mco(m.M, m.rowptr, m.colind, m.values, skip_zero_values=True)
+    rc = oracle_mod.ref_pack_mco(m.M, m.K, m.rowptr, m.colind, m.values)
+    assert mc["T"] == rc["T"] and mc["nval"] == rc["nval"]
+    for k in ("val_soff", "val_sidx", "val_mco_off", "val_mco_mask", "val_mco_val"):
+        assert np.array_equal(BITS(mc[k]), BITS(rc[k])), (name, k)
     for wl in (64, 5):
         for a, b in zip(oracle_mod.strict_lb_plan(m.M, sr["val_soff"], wl),
                         oracle_mod.ref_strict_lb_plan(m.M, sr["val_soff"], wl)):
