@@ -299,7 +299,7 @@ def main():
     ap.add_argument("--workload", default="rmat20_gcn")
     ap.add_argument("--scale", type=int, default=None, help="shrink the workload (R-MAT scale / grid / n)")
     ap.add_argument("--n", type=int, default=512, help="columns of B")
-    ap.add_argument("--format", default="srbcrs", choices=["srbcrs", "metcf"])
+    ap.add_argument("--format", default="srbcrs", choices=["srbcrs", "metcf", "mco"])
     ap.add_argument("--policy", default="auto")
     ap.add_argument("--group-tiles", type=int, default=0)
     ap.add_argument("--hints", type=int, default=0, help="kernel variant: L2 eviction hints bitmask")
@@ -373,8 +373,7 @@ def main():
 
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    packed = engine.pack_srbcrs(rp, ci, va, panel.M, panel.K) if args.format == "srbcrs" else \
-        engine.pack_metcf(rp, ci, va, panel.M, panel.K)
+    packed = {"srbcrs": engine.pack_srbcrs, "metcf": engine.pack_metcf, "mco": engine.pack_mco}[args.format](rp, ci, va, panel.M, panel.K)
     torch.cuda.synchronize()
     pack_ms = (time.perf_counter() - t0) * 1e3
     plan = engine.Plan(packed.val_soff, panel.M, packed.T, args.policy, args.group_tiles)
@@ -483,14 +482,18 @@ def main():
     W = (panel.M + 15) // 16
     distinct = int(np.unique(panel.colind).size)
     G_rows = int(packed.T) * 8  # upper bound of rows fetched without inter-window reuse (incl. padding)
-    bytes_alg = algorithmic_bytes(packed.T, W, panel.M, N, distinct) if args.format == "srbcrs" else \
-        8 * packed.nnz_pad + 4 * (2 * packed.T + 1) + 4 * (8 * packed.T + W + 1) + 4 * N * distinct + 4 * panel.M * N
+    if args.format == "srbcrs":
+        bytes_alg = algorithmic_bytes(packed.T, W, panel.M, N, distinct)
+    elif args.format == "metcf":
+        bytes_alg = 8 * packed.nnz_pad + 4 * (2 * packed.T + 1) + 4 * (8 * packed.T + W + 1) + 4 * N * distinct + 4 * panel.M * N
+    else:  # MCO: 16 B of mask and one offset per tile, the compact values
+        bytes_alg = 4 * packed.nval + 20 * packed.T + 4 + 4 * (8 * packed.T + W + 1) + 4 * N * distinct + 4 * panel.M * N
     kernel_ms = float(np.mean(per_launch))
     achieved = bytes_alg / (kernel_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
                 "traffic": NCU_TRAFFIC_BYTES.get((args.workload, args.scale, N, args.format)) if world == 1 else None,
                 "peak_source": peak_src, "bytes_algorithmic": bytes_alg,
-                "kernel_ms": kernel_ms, "kernel": ("spmm_umma_kernel" if (args.umma and (N % 512 == 0 or (args.format == "metcf" and N % 128 == 0))) else "spmm_async_kernel") + " (+ spmm_fixup_kernel)",
+                "kernel_ms": kernel_ms, "kernel": ("spmm_umma_kernel" if (args.umma and (N % 512 == 0 or (args.format != "srbcrs" and N % 128 == 0))) else "spmm_async_kernel") + " (+ spmm_fixup_kernel)",
                 "bytes_gather_no_reuse": bytes_alg - 4 * N * distinct + 4 * N * G_rows,
                 "padded_tile_tflop": 256.0 * packed.T * N / 1e12,
                 "tf32_dense_peak_tflops_measured": tf32_tflops,
@@ -570,7 +573,7 @@ def main():
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "tf32", "data": "synthetic",
             "config": {"workload": args.workload + (f" scale={args.scale}" if args.scale else ""), "M": m.M, "K": m.K,
-                       "nnz": m.nnz, "N": N, "format": "SR-BCRS 16x8" if args.format == "srbcrs" else "ME-TCF",
+                       "nnz": m.nnz, "N": N, "format": {"srbcrs": "SR-BCRS 16x8", "metcf": "ME-TCF", "mco": "MCO / BIT-TCF"}[args.format],
                        "tiles_rank0": packed.T, "policy": args.policy, "plan": info, "pack_ms_rank0": pack_ms,
                        "partition": "row panels on window boundaries balanced by tiles + 5 per window, B replicated" if world > 1 else "none",
                        "panel_rows": [bounds[i + 1] - bounds[i] for i in range(world)],
