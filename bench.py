@@ -298,7 +298,7 @@ def main():
     ap.add_argument("--impl", default="mask_b200", choices=["mask_b200", "reference"])
     ap.add_argument("--workload", default="rmat20_gcn")
     ap.add_argument("--scale", type=int, default=None, help="shrink the workload (R-MAT scale / grid / n)")
-    ap.add_argument("--n", type=int, default=512, help="columns of B")
+    ap.add_argument("--n", "--cols", dest="n", type=int, default=512, help="columns of B (use --cols under torchrun, whose own parser claims --n)")
     ap.add_argument("--format", default="srbcrs", choices=["srbcrs", "metcf", "mco"])
     ap.add_argument("--policy", default="auto")
     ap.add_argument("--group-tiles", type=int, default=0)
