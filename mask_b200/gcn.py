@@ -123,51 +123,88 @@ class FusedGCN2:
 
     H1 is double-buffered: a rank that races ahead into the next forward writes the other buffer,
     and cannot get a second forward ahead because of the barrier, so no rank's layer-2 reads are
-    overwritten."""
+    overwritten.
 
-    def __init__(self, csr, rank: int, world: int, device, win_prefix, hidden: int, group=None):
-        from . import engine
-        from .peer import PeerBuffer
-        self.engine = engine
+    ``ops`` supplies the three device-specific pieces, so that the protocol (panels, buffer
+    rotation, barrier placement) also runs on CPU ranks in the tests:
+      ops.pack(csr_rows) -> packed
+      ops.shared_h1(rows, cols) -> list of two objects with ``.local`` (this rank's full copy)
+      ops.spmm_to_all(packed, dense, h1_buffer, r0, r1)   # ReLU(A_panel·dense) -> rows [r0,r1) of EVERY rank's copy
+      ops.spmm(packed, dense) -> Tensor                    # plain product of the panel
+      ops.close()
+    """
+
+    def __init__(self, csr, rank: int, world: int, device, win_prefix, hidden: int, group=None, ops=None):
         self.M, self.K, self.rank, self.world, self.group = csr.M, csr.K, rank, world, group
         if csr.M != csr.K:
             raise RuntimeError("the GCN forward needs a square adjacency matrix")
         self.bounds = balanced_panels(np.asarray(win_prefix), csr.M, world)
         self.r0, self.r1 = self.bounds[rank], self.bounds[rank + 1]
-        pack, _ = device_ops(device)
-        self.packed = pack(csr.row_slice(self.r0, self.r1)) if self.r1 > self.r0 else None
+        self.ops = ops if ops is not None else _FusedDeviceOps(device, rank, world, group)
+        self.packed = self.ops.pack(csr.row_slice(self.r0, self.r1)) if self.r1 > self.r0 else None
         self.hidden = hidden
-        self.h1 = [PeerBuffer((csr.M, hidden), device, rank, world, group) for _ in range(2)]
-        self.plans = []
-        if self.packed is not None:
-            for b in self.h1:
-                plan = self.packed.new_plan()
-                if world > 1:
-                    plan.set_peer_outputs(b.others(self.r0 * hidden * 4))
-                self.plans.append(plan)
+        self.h1 = self.ops.shared_h1(csr.M, hidden)
         self.flag = torch.zeros(1, dtype=torch.int32, device=device)
         self.step = 0
+
+    @property
+    def plans(self):
+        return getattr(self.ops, "plans", [])
 
     def forward(self, X: torch.Tensor, W1: torch.Tensor, W2: torch.Tensor) -> torch.Tensor:
         """Returns this rank's rows [bounds[rank], bounds[rank+1]) of the output."""
         if W1.shape[1] != self.hidden:
             raise RuntimeError("W1 does not match the hidden width this object was built for")
         XW1 = X @ W1
-        b = self.step & 1
+        buf = self.h1[self.step & 1]
         self.step += 1
-        h1 = self.h1[b].local
         if self.packed is not None:
-            self.engine.spmm(self.packed, XW1, out=h1[self.r0:self.r1], relu=True, plan=self.plans[b])
+            self.ops.spmm_to_all(self.packed, XW1, buf, self.r0, self.r1)
         if self.world > 1:
-            dist.all_reduce(self.flag, group=self.group)   # stream-ordered barrier: every panel of H1 has landed
+            dist.all_reduce(self.flag, group=self.group)   # (stream-ordered) barrier: every panel of H1 has landed
         if self.packed is None:
             return X.new_zeros((0, W2.shape[1]))
-        return self.engine.spmm(self.packed, h1) @ W2
+        return self.ops.spmm(self.packed, buf.local) @ W2
 
     def close(self) -> None:
-        self.plans = []
-        for b in self.h1:
+        self.ops.close()
+
+
+class _FusedDeviceOps:
+    """The product path of FusedGCN2: device format builder, one plan per H1 buffer with the peers'
+    addresses attached (`mask_plan_set_peer_outputs`), buffers from `mask_peer_alloc`."""
+
+    def __init__(self, device, rank, world, group):
+        from . import engine
+        self.engine, self.device, self.rank, self.world, self.group = engine, device, rank, world, group
+        self.plans, self.buffers, self._by_buffer = [], [], {}
+
+    def pack(self, csr):
+        return device_ops(self.device)[0](csr)
+
+    def shared_h1(self, rows, cols):
+        from .peer import PeerBuffer
+        self.buffers = [PeerBuffer((rows, cols), self.device, self.rank, self.world, self.group) for _ in range(2)]
+        return self.buffers
+
+    def spmm_to_all(self, packed, dense, buf, r0, r1):
+        plan = self._by_buffer.get(id(buf))
+        if plan is None:
+            plan = packed.new_plan()
+            if self.world > 1:
+                plan.set_peer_outputs(buf.others(r0 * dense.shape[1] * 4))
+            self._by_buffer[id(buf)] = plan
+            self.plans.append(plan)
+        self.engine.spmm(packed, dense, out=buf.local[r0:r1], relu=True, plan=plan)
+
+    def spmm(self, packed, dense):
+        return self.engine.spmm(packed, dense)
+
+    def close(self):
+        self.plans, self._by_buffer = [], {}
+        for b in self.buffers:
             b.close()
+        self.buffers = []
 
 
 class _null:

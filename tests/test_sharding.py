@@ -93,6 +93,90 @@ def test_sharded_gcn_forward_matches_single_process(world, chunks):
     assert np.allclose(full, want, rtol=1e-5, atol=1e-6)
 
 
+class _SharedBuf:
+    def __init__(self, copies, rank):
+        self.copies, self.local = copies, copies[rank]
+
+
+class _CpuFusedOps:
+    """FusedGCN2's device pieces on CPU ranks: the ranks' copies of H1 are shared-memory tensors,
+    and 'storing to the peers' is writing the panel's rows into every copy."""
+
+    def __init__(self, rank, shared, delay):
+        self.rank, self.shared, self.delay = rank, shared, delay   # shared[b][rank] = tensor [M, hidden]
+        self.pack, self._spmm = _cpu_ops()
+
+    def shared_h1(self, rows, cols):
+        return [_SharedBuf(self.shared[b], self.rank) for b in range(2)]
+
+    def spmm_to_all(self, csr, dense, buf, r0, r1):
+        import time
+        rows = self._spmm(csr, dense, True)
+        for i, copy in enumerate(buf.copies):
+            if self.delay and i != self.rank:
+                time.sleep(self.delay)    # a slow link: the barrier, not luck, must cover it
+            copy[r0:r1] = rows
+
+    def spmm(self, csr, dense):
+        return self._spmm(csr, dense.clone(), False)
+
+    def close(self):
+        pass
+
+
+def _fused_rank_main(rank, world, port, shared, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from mask_b200.gcn import FusedGCN2
+        from mask_b200.sharding import spmm_cost_prefix
+        import oracle
+        m = G.rmat_gcn_normalised(scale=9, samples_per_node=6, seed=501)
+        X = torch.from_numpy(G.dense_normal(m.K, 24, 502))
+        W1 = torch.from_numpy(G.glorot_uniform(24, 16, 503))
+        W2 = torch.from_numpy(G.glorot_uniform(16, 8, 504))
+        prefix = spmm_cost_prefix(oracle.pack_srbcrs(m.M, m.rowptr, m.colind, m.values)["val_soff"])
+        net = FusedGCN2(m, rank, world, torch.device("cpu"), prefix, hidden=16,
+                        ops=_CpuFusedOps(rank, shared, delay=0.05 if rank == 0 else 0.0))
+        outs = [net.forward(X * s, W1, W2).numpy() for s in (1.0, -2.0, 1.0, 3.0)]
+        q.put((rank, net.bounds, outs))
+        net.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_fused_gcn_protocol_on_cpu_ranks(world):
+    """Panels, H1 double-buffering and barrier placement of FusedGCN2 with gloo ranks whose
+    'peer stores' go to shared-memory copies; one rank's stores are slow.  Four forwards with
+    different inputs reuse both buffers twice."""
+    import oracle
+    m = G.rmat_gcn_normalised(scale=9, samples_per_node=6, seed=501)
+    X = G.dense_normal(m.K, 24, 502)
+    W1, W2 = G.glorot_uniform(24, 16, 503), G.glorot_uniform(16, 8, 504)
+    wants = []
+    for s in (1.0, -2.0, 1.0, 3.0):
+        h1 = np.maximum(oracle.spmm_f32(m.M, m.rowptr, m.colind, m.values, (X * s) @ W1, threads=1), 0)
+        wants.append(oracle.spmm_f32(m.M, m.rowptr, m.colind, m.values, h1, threads=1) @ W2)
+    shared = [[torch.full((m.M, 16), float("nan")).share_memory_() for _ in range(world)] for _ in range(2)]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_fused_rank_main, args=(r, world, port, shared, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=180) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for i, want in enumerate(wants):
+        full = np.zeros_like(want)
+        for rank, bounds, outs in got:
+            full[bounds[rank]:bounds[rank + 1]] = outs[i]
+        assert np.allclose(full, want, rtol=1e-4, atol=1e-5), i
+
+
 def _gpu_rank_main(rank, world, port, q):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
