@@ -286,6 +286,24 @@ def run_bridge(args, m):
                                       "cusparse_ms": rep["timing"]["cusparse_ms"], "passed": rep["correctness"]["passed"],
                                       "max_abs_error": rep["correctness"]["max_abs_error"], "tiles": rep["packed"]["tiles"]}
                 os.remove(js)
+        # the ME-TCF testbed with its generated-operator host program (prints mykernel_time / VERIFICATION)
+        for label, exe in (("dtc_testbed_reference_operator_tile64", "dtc_generated_ref"), ("dtc_testbed_sm100_operator_tile64", "dtc_generated_sm100")):
+            path = os.path.join(here, "oracle", "_ref", exe)
+            if not os.path.exists(path):
+                out[label] = {"unavailable": "not built (needs a checkout of the reference)"}
+                continue
+            r = subprocess.run([path, "-filename", mtx, "-N", str(args.n), "-warmup", str(max(args.warmup, 3)), "-repeat", str(args.steps)],
+                               capture_output=True, text=True, env=dict(os.environ, SPARSENE_DISABLE_MTX_CACHE="1"))
+            rec = {"exit_code": r.returncode}
+            for line in r.stdout.splitlines():
+                if line.startswith("mykernel_time:"):
+                    rec["ms"] = float(line.split()[1])
+                    rec["gflops"] = 2.0 * m.nnz * args.n / (rec["ms"] * 1e-3) / 1e9
+                if line.startswith("cusparse_time:"):
+                    rec["cusparse_ms"] = float(line.split()[1])
+                if line.startswith("VERIFICATION"):
+                    rec["verification"] = line[len("VERIFICATION "):]
+            out[label] = rec
     print(json.dumps({"metric": "SpMM through the reference's Format-DSL bridge executable, kernel ms", "unit": "ms", "n_gpus": 1,
                       "config": {"workload": args.workload, "M": m.M, "nnz": m.nnz, "N": args.n}, "bridge": out}), flush=True)
 

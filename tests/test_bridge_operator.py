@@ -79,3 +79,41 @@ def test_fast_tf32_switch_matches_the_emitted_operator(tmp_path, policy):
     assert a["packed"] == b["packed"]
     assert a["correctness"]["nonfinite"] == 0
     assert a["correctness"]["max_abs_error"] <= 2.0 * b["correctness"]["max_abs_error"] + 1e-4
+
+
+def _run_dtc(exe, mtx, n):
+    env = dict(os.environ, SPARSENE_DISABLE_MTX_CACHE="1")
+    r = subprocess.run([exe, "-filename", mtx, "-N", str(n), "-warmup", "1", "-repeat", "2"], capture_output=True, text=True,
+                       timeout=300, env=env)
+    out = {}
+    for line in r.stdout.splitlines():
+        if line.startswith("VERIFICATION"):
+            out.update({kv.split("=")[0]: float(kv.split("=")[1]) for kv in line.split()[1:]})
+        if line.startswith("mykernel_time:"):
+            out["ms"] = float(line.split()[1])
+    return r, out
+
+
+def test_metcf_operator_declares_the_seam():
+    src = open(os.path.join(ROOT, "include", "mask_b200_operator_metcf_sm100.inc")).read()
+    for token in ("#define SPARSENE_GENERATED_TILE_B", "CHECK_CUDA2", "generated_kernel(float* dB_val, float* dC, int* dval_coo_idx_new"):
+        assert token in src
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [128, 96, 48])      # the host program picks TILE_B = 64, 32, 16
+@pytest.mark.parametrize("name", ["hub_rows", "rmat10", "m33_empty_window", "stencil8", "uniform512"])
+def test_dtc_generated_seam_accepts_the_sm100_operator(tmp_path, name, n):
+    """The reference's ME-TCF testbed (its main, packer, timing loop and cuSPARSE gate, atol = rtol
+    = 1e-3) built with the hand-written operator include: exit code 0 = its verification passed;
+    the same binary with the include kept in the reference tree is run beside it."""
+    ours, theirs = _exe("dtc_generated_sm100"), _exe("dtc_generated_ref")
+    m = cases.SMALL[name]()
+    mtx = str(tmp_path / "m.mtx")
+    G.write_matrix_market(m, mtx)
+    r, a = _run_dtc(ours, mtx, n)
+    r2, b = _run_dtc(theirs, mtx, n)
+    assert "errors" in a and "ms" in a, r.stdout[-1500:] + r.stderr[-1500:]
+    assert a["nonfinite"] == 0
+    assert (r.returncode == 0 and a["errors"] == 0) or r2.returncode != 0, (a, b, r.stdout[-800:])
+    assert a["max_abs_error"] <= 2.0 * b.get("max_abs_error", 0.0) + 1e-4
