@@ -142,8 +142,9 @@ def panel_bounds(m, parts: int, dev) -> list[int]:
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the dominant kernel,
 # captured once with ncu on exactly this workload on one GPU; keyed by (workload, scale, N, format).
 NCU_TRAFFIC_BYTES = {
-    ("rmat20_gcn", None, 512, "srbcrs"): 17.27e9 + 2.21e9,   # profiles/spmm_umma_kernel_n512.md
-    ("rmat20_gcn", 18, 512, "srbcrs"): 2.616e9 + 0.558e9,
+    ("rmat20_gcn", None, 512, "srbcrs"): 17.32e9 + 2.25e9,   # profiles/spmm_umma_kernel_n512.md
+    ("rmat20_gcn", 18, 512, "srbcrs"): 2.596e9 + 0.540e9,
+    ("stencil27_100", None, 512, "srbcrs"): 4.796e9 + 2.070e9,
 }
 
 
