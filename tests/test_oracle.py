@@ -142,3 +142,16 @@ def test_reorders_match_reference_build(oracle_mod, name):
         a = oracle_mod.reorder_rows(kind, m.M, m.K, m.rowptr, m.colind)
         assert np.array_equal(a, oracle_mod.ref_reorder_rows(kind, m.M, m.K, m.rowptr, m.colind)), kind
         assert sorted(a.tolist()) == list(range(m.M))
+
+
+def test_matrix_market_writer_round_trip(tmp_path):
+    """The pattern file the reference's testbeds and bridge read: 1-based coordinates, row-major."""
+    import scipy.io
+    from mask_b200 import generators as G
+    m = cases.SMALL["m33_empty_window"]()
+    path = str(tmp_path / "m.mtx")
+    G.write_matrix_market(m, path)
+    a = scipy.io.mmread(path).tocsr()
+    a.sort_indices()
+    assert a.shape == (m.M, m.K) and a.nnz == m.nnz
+    assert np.array_equal(a.indptr, m.rowptr) and np.array_equal(a.indices, m.colind)
