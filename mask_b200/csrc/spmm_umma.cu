@@ -147,10 +147,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 __device__ __forceinline__ void cp16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
-// with an L2 eviction-priority policy (createpolicy)
-__device__ __forceinline__ void cp16_policy(uint32_t dst, const void* src, uint64_t policy) {
-    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "l"(policy) : "memory");
-}
 
 // METCF: the tile operand is rebuilt per tile from its COO run (examples/src_fp32/dtc/testbed/
 // kernel.inc:822-840 does the same in its shared-memory restore step).  ME-TCF's index
@@ -232,15 +228,6 @@ __global__ void __launch_bounds__(kUmmaThreads, MIN_BLOCKS) spmm_umma_kernel(con
         const char* Bcol = reinterpret_cast<const char*>(p.B + col0 + 32 * pw + 4 * lc);
         const uint32_t ldb_bytes = (uint32_t)(p.ldb * 4);
         const int* ids = reinterpret_cast<const int*>(gbase + L::kIds);
-        // experiment (hints bits 3-4, threshold in bits 8-15): rows of B whose id has few one-bits --
-        // the popular columns of an R-MAT graph -- are copied with evict_last, the others plainly
-        // (bit 4: with evict_first), so that the popular rows stay in L2
-        const int hot_mode = (p.hints >> 3) & 3, hot_thr = (p.hints >> 8) & 0xff;
-        uint64_t pol_keep = 0, pol_stream = 0;
-        if (hot_mode) {
-            asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol_keep));
-            asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol_stream));
-        }
         int s = 0, rel = 0;
         uint32_t round = 0;
         bool ok = true;
@@ -253,24 +240,8 @@ __global__ void __launch_bounds__(kUmmaThreads, MIN_BLOCKS) spmm_umma_kernel(con
 #pragma unroll
                 for (int u = 0; u < KB; u++) {
                     if (u < cnt) {
-                        const int id0 = ids[(rel + u) * kTileCols + lr], id1 = ids[(rel + u) * kTileCols + lr + 4];
-                        const char* r0 = Bcol + (uint64_t)(uint32_t)id0 * ldb_bytes;
-                        const char* r1 = Bcol + (uint64_t)(uint32_t)id1 * ldb_bytes;
-                        if (hot_mode) {
-                            const bool h0 = __popc(id0) <= hot_thr, h1 = __popc(id1) <= hot_thr;
-                            const bool plain = !(hot_mode & 2);
-#pragma unroll
-                            for (int sl = 0; sl < NSLAB; sl++) {
-                                const uint32_t d0 = dst + (u * NSLAB + sl) * 4096 + off0, d1 = dst + (u * NSLAB + sl) * 4096 + off1;
-                                if (h0) cp16_policy(d0, r0 + sl * 512, pol_keep);
-                                else if (plain) cp16(d0, r0 + sl * 512);
-                                else cp16_policy(d0, r0 + sl * 512, pol_stream);
-                                if (h1) cp16_policy(d1, r1 + sl * 512, pol_keep);
-                                else if (plain) cp16(d1, r1 + sl * 512);
-                                else cp16_policy(d1, r1 + sl * 512, pol_stream);
-                            }
-                            continue;
-                        }
+                        const char* r0 = Bcol + (uint64_t)(uint32_t)ids[(rel + u) * kTileCols + lr] * ldb_bytes;
+                        const char* r1 = Bcol + (uint64_t)(uint32_t)ids[(rel + u) * kTileCols + lr + 4] * ldb_bytes;
 #pragma unroll
                         for (int sl = 0; sl < NSLAB; sl++) {
                             cp16(dst + (u * NSLAB + sl) * 4096 + off0, r0 + sl * 512);
