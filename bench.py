@@ -163,7 +163,7 @@ def run_reference(args):
     m, bseed = build_workload(args.workload, args.scale)
     N = args.n
     B = G.dense_normal(m.K, N, bseed)
-    threads = oracle.max_threads()
+    threads = host_threads()
     L = oracle.lib()
     Cm = np.zeros((m.M, N), dtype=np.float32)
 
@@ -197,6 +197,15 @@ def run_reference(args):
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }), flush=True)
+
+
+def host_threads() -> int:
+    """Threads for the CPU arm: every core this process may run on.  torchrun exports
+    OMP_NUM_THREADS=1 for its workers, which must not shrink the CPU baseline to one core."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
 
 
 def run_gcn(args, m, bseed, dev, rank, world):
@@ -524,7 +533,7 @@ def main():
     verified = None
     if world == 1 and not args.no_cpu:
         import oracle
-        threads = oracle.max_threads()
+        threads = host_threads()
         Lo = oracle.lib()
         Cref = np.zeros((m.M, N), dtype=np.float32)
         t0 = time.perf_counter()
