@@ -117,3 +117,19 @@ def test_dtc_generated_seam_accepts_the_sm100_operator(tmp_path, name, n):
     assert a["nonfinite"] == 0
     assert (r.returncode == 0 and a["errors"] == 0) or r2.returncode != 0, (a, b, r.stdout[-800:])
     assert a["max_abs_error"] <= 2.0 * b.get("max_abs_error", 0.0) + 1e-4
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,n", [("hub_rows", 128), ("rmat10", 512), ("m33_empty_window", 64), ("stencil8", 256)])
+def test_srbcrs_testbed_seam(tmp_path, name, n):
+    """The reference's SR-BCRS testbed main (MatrixMarket reader, its own SR-BCRS packer, cuSPARSE
+    check with atol = rtol = 1e-3) linked against libmask_b200.so through the replacement host
+    program mask_b200/seams/sr_bcrs_host_program_16x8.cu: the seam sr_bcrs_test_tf32<16,64,8>."""
+    exe = _exe("srbcrs_testbed_sm100")
+    m = cases.SMALL[name]()
+    mtx = str(tmp_path / "m.mtx")
+    G.write_matrix_market(m, mtx)
+    r = subprocess.run([exe, "-filename", mtx, "-N", str(n), "-warmup", "1", "-repeat", "2"], capture_output=True, text=True,
+                       timeout=300)
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
+    assert "correctness: PASS" in r.stdout and "mykernel_time:" in r.stdout
