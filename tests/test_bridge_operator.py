@@ -133,3 +133,18 @@ def test_srbcrs_testbed_seam(tmp_path, name, n):
                        timeout=300)
     assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
     assert "correctness: PASS" in r.stdout and "mykernel_time:" in r.stdout
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,n", [("hub_rows", 128), ("rmat10", 512), ("m33_empty_window", 48), ("stencil8", 96)])
+def test_dtc_testbed_seam(tmp_path, name, n):
+    """The reference's ME-TCF testbed main (its ME-TCF packer and cuSPARSE check) linked against
+    libmask_b200.so through mask_b200/seams/dtc_host_program.cu: the seam
+    dtc_spmm_test_val_sidx_bind_reorder<TILE_B>."""
+    exe = _exe("dtc_testbed_sm100")
+    m = cases.SMALL[name]()
+    mtx = str(tmp_path / "m.mtx")
+    G.write_matrix_market(m, mtx)
+    r, a = _run_dtc(exe, mtx, n)
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
+    assert a["errors"] == 0 and a["nonfinite"] == 0 and "ms" in a
