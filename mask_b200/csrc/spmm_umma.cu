@@ -53,6 +53,7 @@ constexpr int kUmmaThreads = 352;
 constexpr int kUmmaABytes = 512;
 constexpr int kUmmaIdsBytes = kUmmaMaxGroupTiles * kTileCols * 4;
 constexpr long long kUmmaWaitCycles = 2000000000LL;
+constexpr uint32_t kUmmaSuspendHintNs = 20000;   // upper bound of one try_wait's sleep; completion of the phase wakes the thread at once
 
 // A ring stage holds U "units" of 8 gathered rows x 128 columns (4 KB each):
 //   KB == 1: the NSLAB column slabs of ONE tile (block = 128*NSLAB columns wide),
@@ -96,9 +97,9 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kUmmaSuspendHintNs)
         : "memory");
     return ok != 0;
 }
