@@ -149,6 +149,32 @@ __device__ __forceinline__ void cp16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 
+// The same copy with compile-time offsets folded into the instruction's address immediates.
+template <int DST_IMM, int SRC_IMM>
+__device__ __forceinline__ void cp16_imm(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0 + %2], [%1 + %3], 16;" ::"r"(dst), "l"(src), "n"(DST_IMM), "n"(SRC_IMM) : "memory");
+}
+// Rows r0 / r1 (= row + 4) of one unit group: the same 16-byte chunk of every 128-column slab.
+template <int NSLAB, int U, int SL = 0>
+struct CopySlabs {
+    static __device__ __forceinline__ void run(uint32_t dst0, const char* r0, const char* r1) {
+        cp16_imm<(U * NSLAB + SL) * 4096, SL * 512>(dst0, r0);
+        cp16_imm<(U * NSLAB + SL) * 4096 + 512, SL * 512>(dst0, r1);
+        if constexpr (SL + 1 < NSLAB) CopySlabs<NSLAB, U, SL + 1>::run(dst0, r0, r1);
+    }
+};
+template <int NSLAB, int KB, int U = 0>
+struct CopyUnits {
+    static __device__ __forceinline__ void run(uint32_t dst0, const int* ids, int cnt, int lr, const char* Bcol, uint32_t ldb_bytes) {
+        if (U < cnt) {
+            const char* r0 = Bcol + (uint64_t)(uint32_t)ids[U * kTileCols + lr] * ldb_bytes;
+            const char* r1 = Bcol + (uint64_t)(uint32_t)ids[U * kTileCols + lr + 4] * ldb_bytes;
+            CopySlabs<NSLAB, U>::run(dst0, r0, r1);
+        }
+        if constexpr (U + 1 < KB) CopyUnits<NSLAB, KB, U + 1>::run(dst0, ids, cnt, lr, Bcol, ldb_bytes);
+    }
+};
+
 // METCF: the tile operand is rebuilt per tile from its COO run (examples/src_fp32/dtc/testbed/
 // kernel.inc:822-840 does the same in its shared-memory restore step).  ME-TCF's index
 // Swizzle<1,2,3>(8r+c) is exactly the K-major SWIZZLE_32B operand layout, so tile[idx] = value
@@ -225,7 +251,6 @@ __global__ void __launch_bounds__(kUmmaThreads, MIN_BLOCKS) spmm_umma_kernel(con
         const int pw = warp - 7;                 // this warp copies 32-column atom pw of every unit
         const int lr = lane >> 3, lc = lane & 7; // row (and row + 4), 16-byte chunk
         const uint32_t off0 = (uint32_t)(pw * 1024 + lr * 128 + ((lc ^ (2 * lr)) * 16));   // 32-byte chunks swizzled by row % 4
-        const uint32_t off1 = off0 + 512;                                                 // row + 4: same swizzle phase
         const char* Bcol = reinterpret_cast<const char*>(p.B + col0 + 32 * pw + 4 * lc);
         const uint32_t ldb_bytes = (uint32_t)(p.ldb * 4);
         const int* ids = reinterpret_cast<const int*>(gbase + L::kIds);
@@ -237,19 +262,8 @@ __global__ void __launch_bounds__(kUmmaThreads, MIN_BLOCKS) spmm_umma_kernel(con
             for (int i = 0; i < n; i += KB) {
                 const int cnt = min(KB, n - i);
                 if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag)) { ok = false; break; }
-                const uint32_t dst = base + L::kB + s * L::kBBytes;
-#pragma unroll
-                for (int u = 0; u < KB; u++) {
-                    if (u < cnt) {
-                        const char* r0 = Bcol + (uint64_t)(uint32_t)ids[(rel + u) * kTileCols + lr] * ldb_bytes;
-                        const char* r1 = Bcol + (uint64_t)(uint32_t)ids[(rel + u) * kTileCols + lr + 4] * ldb_bytes;
-#pragma unroll
-                        for (int sl = 0; sl < NSLAB; sl++) {
-                            cp16(dst + (u * NSLAB + sl) * 4096 + off0, r0 + sl * 512);
-                            cp16(dst + (u * NSLAB + sl) * 4096 + off1, r1 + sl * 512);
-                        }
-                    }
-                }
+                // off1 = off0 + 512: both rows of a thread go through one base register plus immediates
+                CopyUnits<NSLAB, KB>::run(base + L::kB + s * L::kBBytes + off0, ids + rel * kTileCols, cnt, lr, Bcol, ldb_bytes);
                 // tile operand(s): warp u copies the one of tile u of the step
                 if (pw < cnt) {
                     const int tile = rel + pw;
