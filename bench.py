@@ -19,6 +19,15 @@ One JSON line is printed by rank 0:
   cpu_baseline  the host FP32 reference SpMM (CPU port of the reference's cpu_spmm) timed on this
              box's cores on the same matrix (rank 0, N=1 only); also used to verify the GPU result
 --impl reference times that CPU implementation alone, with all host threads.
+
+Extra lines on request (each prints its own JSON line instead of the one above):
+  --gcn [--gcn-fused]   row-sharded 2-layer GCN forward; fused = the layer-1 SpMM stores H1 into every
+                        rank's copy through peer memory instead of NCCL broadcasts
+  --bridge              the reference's Format-DSL bridge and ME-TCF testbed executables (built by
+                        `make -C oracle bridge` where a checkout of the reference is present) with the
+                        operator the reference emits and with the hand-written sm_100a operator includes
+  --baselines           cuSPARSE CSR and the reference's own kernel recompiled for sm_100a, same inputs
+Other switches: --format srbcrs|metcf|mco, --workload, --scale, --cols (= --n), --policy, kernel knobs.
 """
 from __future__ import annotations
 
