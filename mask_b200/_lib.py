@@ -69,6 +69,7 @@ class Features(C.Structure):
                 ("tiles_p50", i32), ("tiles_p95", i32), ("tiles_p99", i32), ("tiles_max", i32),
                 ("top5_window_share", C.c_double), ("tile_fill", C.c_double), ("heavy_tail", i32)]
 EPILOGUE_NONE, EPILOGUE_RELU = 0, 1
+NUMERICS_TF32X3 = 0x100   # OR-able into the epilogue argument (SR-BCRS)
 
 _lib = None
 

@@ -99,7 +99,8 @@ struct CopyRows {
 // once per 32*NQ-column slab: the rows of B then compete for L2 with 32*NQ*4 bytes each instead of
 // 4N bytes, which is what raises the hit rate on power-law matrices.
 // GUARD = false requires N % (32*NQ*WPB) == 0 (every column group of every warp is full).
-template <int NQ, int S, int MIN_BLOCKS, bool GUARD, int WPB = kWarpsPerBlock>
+// COMP: three products per MMA (hi*hi and the two residual terms), see MASK_NUMERICS_TF32X3.
+template <int NQ, int S, int MIN_BLOCKS, bool GUARD, int WPB = kWarpsPerBlock, bool COMP = false>
 __global__ void __launch_bounds__(WPB * 32, MIN_BLOCKS) spmm_async_kernel(const SpmmArgs p) {
     using L = AsyncLayout<NQ, S, WPB>;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -212,17 +213,37 @@ __global__ void __launch_bounds__(WPB * 32, MIN_BLOCKS) spmm_async_kernel(const 
 
         const unsigned char* slot = wbase + c_slot;
         const unsigned char* at = slot + L::kBBytes;
-        uint32_t a[4] = {rna_bits(*reinterpret_cast<const float*>(at + ao0)), rna_bits(*reinterpret_cast<const float*>(at + ao1)),
-                         rna_bits(*reinterpret_cast<const float*>(at + ao2)), rna_bits(*reinterpret_cast<const float*>(at + ao3))};
+        const float af[4] = {*reinterpret_cast<const float*>(at + ao0), *reinterpret_cast<const float*>(at + ao1),
+                             *reinterpret_cast<const float*>(at + ao2), *reinterpret_cast<const float*>(at + ao3)};
         const unsigned char* bt = slot + frag_off;
+        if constexpr (COMP) {
+            uint32_t a[4], al[4];
 #pragma unroll
-        for (int q = 0; q < NQ; q++) {
-            const float4 v0 = *reinterpret_cast<const float4*>(bt + q * 1024);
-            const float4 v1 = *reinterpret_cast<const float4*>(bt + q * 1024 + 512);
-            mma_tf32(acc[q][0], a, rna_bits(v0.x), rna_bits(v1.x));
-            mma_tf32(acc[q][1], a, rna_bits(v0.y), rna_bits(v1.y));
-            mma_tf32(acc[q][2], a, rna_bits(v0.z), rna_bits(v1.z));
-            mma_tf32(acc[q][3], a, rna_bits(v0.w), rna_bits(v1.w));
+            for (int i = 0; i < 4; i++) { a[i] = tf32_hi(af[i]); al[i] = tf32_lo(af[i], a[i]); }
+#pragma unroll
+            for (int q = 0; q < NQ; q++) {
+                const float4 v0 = *reinterpret_cast<const float4*>(bt + q * 1024);
+                const float4 v1 = *reinterpret_cast<const float4*>(bt + q * 1024 + 512);
+                const float b0[4] = {v0.x, v0.y, v0.z, v0.w}, b1[4] = {v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint32_t h0 = tf32_hi(b0[j]), h1 = tf32_hi(b1[j]);
+                    mma_tf32(acc[q][j], al, h0, h1);                                       // small terms first
+                    mma_tf32(acc[q][j], a, tf32_lo(b0[j], h0), tf32_lo(b1[j], h1));
+                    mma_tf32(acc[q][j], a, h0, h1);
+                }
+            }
+        } else {
+            uint32_t a[4] = {rna_bits(af[0]), rna_bits(af[1]), rna_bits(af[2]), rna_bits(af[3])};
+#pragma unroll
+            for (int q = 0; q < NQ; q++) {
+                const float4 v0 = *reinterpret_cast<const float4*>(bt + q * 1024);
+                const float4 v1 = *reinterpret_cast<const float4*>(bt + q * 1024 + 512);
+                mma_tf32(acc[q][0], a, rna_bits(v0.x), rna_bits(v1.x));
+                mma_tf32(acc[q][1], a, rna_bits(v0.y), rna_bits(v1.y));
+                mma_tf32(acc[q][2], a, rna_bits(v0.z), rna_bits(v1.z));
+                mma_tf32(acc[q][3], a, rna_bits(v0.w), rna_bits(v1.w));
+            }
         }
         t++;
         r_slot = c_slot;
@@ -233,12 +254,12 @@ __global__ void __launch_bounds__(WPB * 32, MIN_BLOCKS) spmm_async_kernel(const 
     cp_async_wait<0>();
 }
 
-template <int NQ, int S, int MIN_BLOCKS, int WPB = kWarpsPerBlock>
+template <int NQ, int S, int MIN_BLOCKS, int WPB = kWarpsPerBlock, bool COMP = false>
 static int launch_variant(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st) {
     using L = AsyncLayout<NQ, S, WPB>;
     const int cols_per_block = 32 * NQ * WPB;
     const bool guard = (a.N % cols_per_block) != 0;
-    auto kern = guard ? spmm_async_kernel<NQ, S, MIN_BLOCKS, true, WPB> : spmm_async_kernel<NQ, S, MIN_BLOCKS, false, WPB>;
+    auto kern = guard ? spmm_async_kernel<NQ, S, MIN_BLOCKS, true, WPB, COMP> : spmm_async_kernel<NQ, S, MIN_BLOCKS, false, WPB, COMP>;
     // opt in to more than 48 KB of dynamic shared memory (cheap; repeated per call so that it
     // holds for whichever device is current)
     MASK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBlockBytes));
@@ -251,6 +272,11 @@ static int launch_variant(const mask_plan* plan, const SpmmArgs& a, cudaStream_t
 
 int launch_spmm_async(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int nq, int stages) {
     if (nq != 1 && nq != 2 && nq != 4) nq = a.N > 256 ? 4 : (a.N > 128 ? 2 : 1);
+    if (a.tf32x3) {   // compensated products: the default variant of each width
+        if (nq == 4) return launch_variant<4, 4, 2, kWarpsPerBlock, true>(plan, a, st);
+        if (nq == 2) return launch_variant<2, 4, 4, kWarpsPerBlock, true>(plan, a, st);
+        return launch_variant<1, 8, 4, kWarpsPerBlock, true>(plan, a, st);
+    }
     // `stages` = S (ring slots per warp) or 10*S + resident blocks per SM for the variants that
     // differ in occupancy.  Shared memory per block = 4 warps x S x (nq + 0.5) KB (+ ids).
     switch (nq) {

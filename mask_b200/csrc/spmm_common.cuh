@@ -28,6 +28,7 @@ struct SpmmArgs {
     int32_t M;
     int32_t N;
     int32_t relu;
+    int32_t tf32x3;  // compensated products (MASK_NUMERICS_TF32X3)
     int32_t hints;   // bit 0: L2 eviction-priority hints on the copies, bit 1: streaming stores of C
 };
 
@@ -40,6 +41,10 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], 
 }
 
 __device__ __forceinline__ uint32_t rna_bits(float x) { return __float_as_uint(x) + 0x1000u; }
+// Split for compensated products: the rounded value itself (low 13 bits cleared) and the TF32
+// operand of what the rounding lost.
+__device__ __forceinline__ uint32_t tf32_hi(float x) { return (__float_as_uint(x) + 0x1000u) & 0xffffe000u; }
+__device__ __forceinline__ uint32_t tf32_lo(float x, uint32_t hi) { return rna_bits(x - __uint_as_float(hi)); }
 
 __device__ __forceinline__ float4 ldg_f4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
 

@@ -323,6 +323,11 @@ static int launch_spmm(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
     // for ME-TCF it beats the register-pipelined kernel at every width.  umma = 2 forces it.
     const bool umma_fits = N % 128 == 0 && plan->max_group_tiles <= kUmmaMaxGroupTiles;
     constexpr bool METCF = FMT != kFmtSrbcrs;   // the COO and bitmap leaves take the same routes
+    if (FMT == kFmtSrbcrs && a.tf32x3) {   // compensated products: mma.sync ring kernel
+        int rc = launch_spmm_async(plan, a, st, 0, 0);
+        if (rc != MASK_OK) return rc;
+        return launch_fixup(plan, a, st);
+    }
     if (umma_fits && (g_tune_umma == 2 || (g_tune_umma == 1 && (METCF || N % 512 == 0)))) {
         int rc = launch_spmm_umma(plan, a, st, g_tune_umma_variant);
         if (rc != MASK_OK) return rc;
@@ -405,7 +410,8 @@ extern "C" int mask_spmm_srbcrs(const mask_plan* plan, const int32_t* d_val_soff
     a.val_blk = d_val_block_val;
     a.B = d_B; a.ldb = ldb; a.C = d_C; a.ldc = ldc;
     a.scratch = static_cast<float*>(d_scratch);
-    a.M = M; a.N = N; a.relu = (epilogue == MASK_EPILOGUE_RELU);
+    a.M = M; a.N = N; a.relu = ((epilogue & 0xff) == MASK_EPILOGUE_RELU);
+    a.tf32x3 = (epilogue & MASK_NUMERICS_TF32X3) ? 1 : 0;
     return launch_spmm<kFmtSrbcrs>(plan, a, static_cast<cudaStream_t>(stream));
 }
 
@@ -424,7 +430,8 @@ extern "C" int mask_spmm_metcf(const mask_plan* plan, const int32_t* d_val_soff,
     a.coo_off = d_val_coo_off; a.coo_idx = d_val_coo_idx; a.coo_val = d_val_coo_val;
     a.B = d_B; a.ldb = ldb; a.C = d_C; a.ldc = ldc;
     a.scratch = static_cast<float*>(d_scratch);
-    a.M = M; a.N = N; a.relu = (epilogue == MASK_EPILOGUE_RELU);
+    a.M = M; a.N = N; a.relu = ((epilogue & 0xff) == MASK_EPILOGUE_RELU);
+    MASK_REQUIRE(!(epilogue & MASK_NUMERICS_TF32X3), "compensated products are implemented for SR-BCRS only");
     return launch_spmm<kFmtMetcf>(plan, a, static_cast<cudaStream_t>(stream));
 }
 
@@ -447,6 +454,7 @@ extern "C" int mask_spmm_mco(const mask_plan* plan, const int32_t* d_val_soff, c
     a.mco_mask = reinterpret_cast<const unsigned long long*>(d_val_mco_mask);
     a.B = d_B; a.ldb = ldb; a.C = d_C; a.ldc = ldc;
     a.scratch = static_cast<float*>(d_scratch);
-    a.M = M; a.N = N; a.relu = (epilogue == MASK_EPILOGUE_RELU);
+    a.M = M; a.N = N; a.relu = ((epilogue & 0xff) == MASK_EPILOGUE_RELU);
+    MASK_REQUIRE(!(epilogue & MASK_NUMERICS_TF32X3), "compensated products are implemented for SR-BCRS only");
     return launch_spmm<kFmtMco>(plan, a, static_cast<cudaStream_t>(stream));
 }

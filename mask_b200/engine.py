@@ -280,8 +280,9 @@ def pack_mco(rowptr, colind, values, M: int, K: int, skip_zero_values: bool = Fa
 
 
 def spmm(packed, dense: torch.Tensor, out: torch.Tensor | None = None, policy: str = "auto", relu: bool = False,
-         plan: Plan | None = None) -> torch.Tensor:
-    """out[M,N] = A @ dense[K,N] on the current stream.  ``out`` is fully overwritten."""
+         plan: Plan | None = None, tf32x3: bool = False) -> torch.Tensor:
+    """out[M,N] = A @ dense[K,N] on the current stream.  ``out`` is fully overwritten.
+    ``tf32x3`` (SR-BCRS): compensated products, FP32-level accuracy at about 1.7x the time."""
     _req(dense, torch.float32, "dense")
     if dense.dim() != 2:
         raise RuntimeError("dense must be 2-D")
@@ -301,7 +302,7 @@ def spmm(packed, dense: torch.Tensor, out: torch.Tensor | None = None, policy: s
         raise RuntimeError("this matrix was packed from reordered rows: use packed.plan() / packed.new_plan()")
     scratch = plan.scratch(N, dense.device)
     sb = 0 if scratch is None else scratch.numel()
-    epi = _lib.EPILOGUE_RELU if relu else _lib.EPILOGUE_NONE
+    epi = (_lib.EPILOGUE_RELU if relu else _lib.EPILOGUE_NONE) | (_lib.NUMERICS_TF32X3 if tf32x3 else 0)
     L = lib()
     if isinstance(packed, PackedMCO):
         check(L.mask_spmm_mco(plan._h, _ptr(packed.val_soff), _ptr(packed.val_sidx), _ptr(packed.val_mco_off),

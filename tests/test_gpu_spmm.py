@@ -355,3 +355,31 @@ def test_peer_outputs_receive_the_same_rows(oracle_mod, name, N, gt, umma, fmt, 
         assert torch.equal(t, out)
     with pytest.raises(_lib.MaskError):
         plan.set_peer_outputs(torch.zeros(16, dtype=torch.int64, device="cuda"))
+
+
+@pytest.mark.parametrize("name", ["m17", "m33_empty_window", "hub_rows", "rmat10", "stencil8", "uniform512"])
+@pytest.mark.parametrize("N", [64, 200, 512])
+def test_tf32x3_compensated_products(oracle_mod, name, N):
+    """MASK_NUMERICS_TF32X3: hi*hi plus the two residual products per MMA.  What is left is the
+    lo*lo term and the rounding of the residuals (about 2^-21 per product) plus FP32 summation
+    order, so the result must sit within 2e-5 * (|A|.|B|) of the host FP32 product -- a hundred
+    times tighter than the single-product contract -- also through ReLU and split windows."""
+    import torch
+    from mask_b200 import engine, _lib
+    m = cases.SMALL[name]()
+    rp, ci, va = _dev(m)
+    p = engine.pack_srbcrs(rp, ci, va, m.M, m.K)
+    B = _dense(m.K, N, 31)
+    Bd = torch.from_numpy(B).cuda()
+    ref = oracle_mod.spmm_f32(m.M, m.rowptr, m.colind, m.values, B)
+    absp = oracle_mod.spmm_abs_f64(m.M, m.rowptr, m.colind, m.values, B)
+    plan = engine.Plan(p.val_soff, m.M, p.T, "auto", 3)
+    for relu in (False, True):
+        out = torch.full((m.M, N), float("nan"), device="cuda")
+        engine.spmm(p, Bd, out=out, plan=plan, relu=relu, tf32x3=True)
+        want = np.maximum(ref, 0) if relu else ref
+        bad, worst = oracle_mod.check_tolerance(out.cpu().numpy(), want, absp, 2e-5, 1e-6)
+        assert bad == 0, f"{bad} elements outside the compensated tolerance, worst ratio {worst}"
+    pm = engine.pack_metcf(rp, ci, va, m.M, m.K)
+    with pytest.raises(_lib.MaskError):
+        engine.spmm(pm, Bd, tf32x3=True)
