@@ -1,5 +1,5 @@
 """Test infrastructure: runs the reference project's own Format -> CUDA compiler (imported from a
-checkout at $MASK_REF, default /root/reference) on its built-in SR-BCRS 16x8 format and writes the
+checkout named by $MASK_REF) on its built-in SR-BCRS 16x8 format and writes the
 emitted operator include to oracle/_ref/gen/operators/sr_bcrs_16x8.inc.  That file is the
 reference-generated kernel the DSL host bridge is built with for same-box comparisons; it is a
 build product of the reference and is not kept in the history.

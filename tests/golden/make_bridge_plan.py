@@ -1,6 +1,6 @@
 """Writes tests/golden/bridge_plans.json: the reference's own ``select_backend`` output for the
 SR-BCRS 16x8 mapping (plain and with each row reorder), imported from a checkout of the reference
-at $MASK_REF (default /root/reference).  tests/test_bridge_host.py compares mask_b200.bridge with it.
+named by $MASK_REF.  tests/test_bridge_host.py compares mask_b200.bridge with it.
 
     python tests/golden/make_bridge_plan.py
 """

@@ -1,6 +1,6 @@
 """Generates tests/golden/*.npz from the REFERENCE project's own host packers and planners.
 
-Run in a container that holds a checkout of the reference project (default /root/reference):
+Run in a container that holds a checkout of the reference project (its path in $MASK_REF):
 
     make -C oracle ref          # builds oracle/_ref/*.so from the reference sources
     python tests/golden/make_golden.py
