@@ -34,7 +34,8 @@ typedef enum mask_status {
     MASK_ERR_SCRATCH_TOO_SMALL = 4,
     MASK_ERR_INDEX_OVERFLOW = 5,   /* a count does not fit the int32 index arrays of the format */
     MASK_ERR_COLUMN_RANGE = 6,     /* a column id is outside [0, K) */
-    MASK_ERR_NO_DEVICE = 7
+    MASK_ERR_NO_DEVICE = 7,
+    MASK_ERR_KERNEL_TIMEOUT = 8    /* a kernel gave up on one of its bounded waits: the output is invalid */
 } mask_status;
 
 int mask_version(void);
@@ -175,7 +176,12 @@ int mask_features_from_soff(const int32_t* h_val_soff, int32_t M, int64_t nnz, m
  * loadCheckpoint (examples/src_fp32/dtc/testbed/main.cu:217-340): raw little-endian
  * [T][nnz_pad][val_soff][val_sidx][val_coo_off][val_coo_idx][val_coo_val]; host arrays.
  * ------------------------------------------------------------------------------------------ */
+/* File name for a matrix known by name (the stem of its file). */
 int mask_metcf_checkpoint_name(const char* matrix_name, int32_t M, int32_t K, char* out, size_t out_len);
+/* File name exactly as the reference testbed derives it from the path it was given
+ * (buildCheckpointStem, main.cu:205-230): stem of `file_path`, or for an empty path (matrix
+ * generated in memory) "synthetic..._sp<sparsity token>". */
+int mask_metcf_checkpoint_name_for(const char* file_path, int32_t M, int32_t K, float sparsity, char* out, size_t out_len);
 int mask_metcf_checkpoint_write(const char* path, int32_t M, int64_t T, int64_t nnz_pad,
                                 const int32_t* val_soff, const int32_t* val_sidx,
                                 const int32_t* val_coo_off, const int32_t* val_coo_idx,
@@ -237,9 +243,13 @@ int mask_peer_alloc(size_t bytes, void** d_ptr, void* handle);
 int mask_peer_open(const void* handle, void** d_ptr);
 int mask_peer_close(void* d_ptr);
 int mask_peer_free(void* d_ptr);
-/* Reads the plan's device status word (synchronises): 0, or non-zero if a kernel launched with
- * this plan gave up on one of its bounded waits (its output is then invalid).  No counterpart in
- * the reference, whose kernels have no waits. */
+/* Reads AND CLEARS the plan's device status word (synchronises the stream): 0, or non-zero if a
+ * kernel launched with this plan since the last call gave up on one of its bounded waits (its
+ * output is then invalid; the kernel has drained its copies and tensor-core work and freed its
+ * tensor memory, so the context stays usable).  The device-pointer SpMM entry points are
+ * asynchronous and cannot report this themselves: call this wherever the host synchronises anyway.
+ * mask_session_spmm_host does so itself and returns MASK_ERR_KERNEL_TIMEOUT.  No counterpart in the
+ * reference, whose kernels have no waits. */
 int mask_plan_status(const mask_plan* plan, int32_t* h_status, void* stream);
 /* Copies the plan tables to host arrays (frag_offset[F+1], frag_window[F], group_offset[G+1]). */
 int mask_plan_export(const mask_plan* plan, int32_t* frag_offset, int32_t* frag_window,
@@ -297,7 +307,9 @@ int mask_spmm_mco(const mask_plan* plan, const int32_t* d_val_soff, const int32_
  *     nothing is launched.
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device current).  Make that first call during start-up,
- *     before any stream capture begins.
+ *     before any stream capture begins.  The address is remembered per device ordinal for the
+ *     device's primary context; it is not valid after cudaDeviceReset or under another context on
+ *     the same ordinal.
  *   - All calls on a device share the one array and it keeps whatever the last call left in it.
  *     Nothing in it needs clearing between calls (each call writes every partial tile before
  *     reading it), but two calls that overlap on the GPU -- different streams, or different
@@ -319,6 +331,20 @@ int mask_spmm_srbcrs_static_scratch(const mask_plan* plan, const int32_t* d_val_
  * the reference's tile_b environment switches SRBCRS_TILE_B / DTC_TILE_B
  * (examples/src_fp32/sr_bcrs/testbed/SRBCRSSpMM_kernel.cu:435-475). */
 int mask_tune(const char* name, int value);
+
+/* Which kernel the SpMM entry points launch for a plan, an encoding (0 SR-BCRS, 1 ME-TCF, 2 MCO), N
+ * and an epilogue argument, as text ("spmm_sweep_kernel<nslab=4,srbcrs>"), and a number that
+ * changes whenever the library's main kernel changes in a way that affects its memory traffic
+ * (measurement harnesses pair captured profiler figures with it).  No counterpart in the
+ * reference. */
+int mask_spmm_kernel_name(const mask_plan* plan, int format, int32_t N, int epilogue, char* out, size_t capacity);
+int mask_kernel_revision(void);
+
+/* cudaMemcpy2DAsync behind the C ABI, for hosts that drive their own upload / product / download
+ * pipeline over column chunks of row-major host matrices (kind: 1 = host to device, 2 = device to
+ * host, 3 = device to device).  Pitches and width in bytes.  No counterpart in the reference. */
+int mask_copy_2d_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
+                       size_t rows, int kind, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Host-buffer seam.  Replaces the testbed entry sr_bcrs_test_tf32<16,64,8>

@@ -35,6 +35,7 @@ SIGNATURES = {
     "mask_peer_free": (C.c_int, [vp]),
     "mask_features_from_soff": (C.c_int, [vp, i32, i64, vp]),
     "mask_metcf_checkpoint_name": (C.c_int, [C.c_char_p, i32, i32, C.c_char_p, sz]),
+    "mask_metcf_checkpoint_name_for": (C.c_int, [C.c_char_p, i32, i32, C.c_float, C.c_char_p, sz]),
     "mask_metcf_checkpoint_write": (C.c_int, [C.c_char_p, i32, i64, i64, vp, vp, vp, vp, vp]),
     "mask_metcf_checkpoint_header": (C.c_int, [C.c_char_p, C.POINTER(i64), C.POINTER(i64)]),
     "mask_metcf_checkpoint_read": (C.c_int, [C.c_char_p, i32, i32, i64, i64, vp, vp, vp, vp, vp]),
@@ -52,6 +53,9 @@ SIGNATURES = {
     "mask_static_scratch_capacity": (sz, []),
     "mask_spmm_srbcrs_static_scratch": (C.c_int, [vp, vp, vp, vp, i32, i32, i32, vp, i64, vp, i64, C.c_int, vp]),
     "mask_tune": (C.c_int, [C.c_char_p, C.c_int]),
+    "mask_spmm_kernel_name": (C.c_int, [vp, C.c_int, i32, C.c_int, C.c_char_p, sz]),
+    "mask_kernel_revision": (C.c_int, []),
+    "mask_copy_2d_async": (C.c_int, [vp, sz, vp, sz, sz, sz, C.c_int, vp]),
     "mask_session_create_srbcrs": (C.c_int, [i32, i32, i64, vp, vp, vp, C.c_int, C.POINTER(vp)]),
     "mask_session_create_csr": (C.c_int, [i32, i32, i64, vp, vp, vp, C.c_int, C.POINTER(vp)]),
     "mask_session_spmm_host": (C.c_int, [vp, vp, vp, i32, C.POINTER(C.c_float)]),
@@ -95,6 +99,11 @@ def lib() -> C.CDLL:
             fn.restype = res
             fn.argtypes = args
         _lib = L
+        # development switch: MASK_B200_TUNE="knob=value,..." applies mask_tune() knobs at load time
+        for item in filter(None, os.environ.get("MASK_B200_TUNE", "").split(",")):
+            name, _, value = item.partition("=")
+            if L.mask_tune(name.strip().encode(), int(value)) != 0:
+                raise RuntimeError(f"MASK_B200_TUNE: unknown knob {name!r}")
     return _lib
 
 

@@ -22,6 +22,18 @@ extern "C" int mask_version(void) { return 100; }
 
 extern "C" const char* mask_last_error(void) { return mask::g_error; }
 
+extern "C" int mask_copy_2d_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
+                                  size_t rows, int kind, void* stream) {
+    using namespace mask;
+    MASK_REQUIRE(dst != nullptr && src != nullptr, "NULL pointer");
+    MASK_REQUIRE(kind >= 1 && kind <= 3, "kind must be 1 (host to device), 2 (device to host) or 3 (device to device)");
+    MASK_REQUIRE(width_bytes <= dst_pitch && width_bytes <= src_pitch, "width exceeds a pitch");
+    if (width_bytes == 0 || rows == 0) return MASK_OK;
+    const cudaMemcpyKind k = kind == 1 ? cudaMemcpyHostToDevice : (kind == 2 ? cudaMemcpyDeviceToHost : cudaMemcpyDeviceToDevice);
+    MASK_CUDA_TRY(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, k, static_cast<cudaStream_t>(stream)));
+    return MASK_OK;
+}
+
 extern "C" const char* mask_status_string(int status) {
     switch (status) {
         case MASK_OK: return "ok";
@@ -32,6 +44,7 @@ extern "C" const char* mask_status_string(int status) {
         case MASK_ERR_INDEX_OVERFLOW: return "count does not fit the format's int32 indices";
         case MASK_ERR_COLUMN_RANGE: return "column id out of range";
         case MASK_ERR_NO_DEVICE: return "no CUDA device";
+        case MASK_ERR_KERNEL_TIMEOUT: return "a kernel gave up on a bounded wait";
         default: return "unknown status";
     }
 }
@@ -85,6 +98,15 @@ static int session_chunk_cols(int32_t N) {
     if (w % 32 != 0 || N % w != 0) w = 128;
     while (N / w > mask_session::kMaxChunks) w *= 2;
     return (N % w == 0 && N / w >= 2) ? w : 0;
+}
+
+// After the session's streams are idle: has a kernel of this call given up on a bounded wait?
+static int session_kernel_status(mask_session* s) {
+    int32_t st = 0;
+    int rc = mask_plan_status(s->plan, &st, s->stream);
+    if (rc != MASK_OK) return rc;
+    if (st != 0) return fail(MASK_ERR_KERNEL_TIMEOUT, "a kernel gave up on a bounded wait; the product is invalid");
+    return MASK_OK;
 }
 
 static int grow(void** p, size_t* have, size_t need) {
@@ -223,25 +245,32 @@ extern "C" int mask_session_spmm_host(mask_session* s, const float* h_B, float* 
     if (w > 0) {
         const int chunks = N / w;
         const size_t pitch = (size_t)N * 4, width = (size_t)w * 4;
-        for (int i = 0; i < chunks; i++) {
-            const size_t c0 = (size_t)i * w;
-            MASK_CUDA_TRY(cudaMemcpy2DAsync(s->d_B + c0, pitch, h_B + c0, pitch, width, (size_t)s->K, cudaMemcpyHostToDevice, s->up));
-            MASK_CUDA_TRY(cudaEventRecord(s->uploaded[i], s->up));
-            MASK_CUDA_TRY(cudaStreamWaitEvent(s->stream, s->uploaded[i], 0));
-            MASK_CUDA_TRY(cudaEventRecord(s->k0[i], s->stream));
-            rc = mask_spmm_srbcrs(s->plan, s->d_soff, s->d_sidx, s->d_blk, s->M, s->K, w, s->d_B + c0, N, s->d_C + c0, N,
-                                  s->d_scratch, s->scratch_bytes, MASK_EPILOGUE_NONE, s->stream);
-            if (rc != MASK_OK) break;
-            MASK_CUDA_TRY(cudaEventRecord(s->k1[i], s->stream));
-            MASK_CUDA_TRY(cudaStreamWaitEvent(s->down, s->k1[i], 0));
-            MASK_CUDA_TRY(cudaMemcpy2DAsync(h_C + c0, pitch, s->d_C + c0, pitch, width, (size_t)s->M, cudaMemcpyDeviceToHost, s->down));
-        }
-        // everything that was enqueued must finish before the caller's buffers are touched again
+        auto enqueue = [&]() -> int {
+            for (int i = 0; i < chunks; i++) {
+                const size_t c0 = (size_t)i * w;
+                MASK_CUDA_TRY(cudaMemcpy2DAsync(s->d_B + c0, pitch, h_B + c0, pitch, width, (size_t)s->K, cudaMemcpyHostToDevice, s->up));
+                MASK_CUDA_TRY(cudaEventRecord(s->uploaded[i], s->up));
+                MASK_CUDA_TRY(cudaStreamWaitEvent(s->stream, s->uploaded[i], 0));
+                MASK_CUDA_TRY(cudaEventRecord(s->k0[i], s->stream));
+                int r = mask_spmm_srbcrs(s->plan, s->d_soff, s->d_sidx, s->d_blk, s->M, s->K, w, s->d_B + c0, N, s->d_C + c0, N,
+                                         s->d_scratch, s->scratch_bytes, MASK_EPILOGUE_NONE, s->stream);
+                if (r != MASK_OK) return r;
+                MASK_CUDA_TRY(cudaEventRecord(s->k1[i], s->stream));
+                MASK_CUDA_TRY(cudaStreamWaitEvent(s->down, s->k1[i], 0));
+                MASK_CUDA_TRY(cudaMemcpy2DAsync(h_C + c0, pitch, s->d_C + c0, pitch, width, (size_t)s->M, cudaMemcpyDeviceToHost, s->down));
+            }
+            return MASK_OK;
+        };
+        rc = enqueue();
+        // whatever was enqueued -- also when enqueueing failed half way -- must finish before the caller's
+        // buffers are touched again
         cudaError_t e1 = cudaStreamSynchronize(s->up), e2 = cudaStreamSynchronize(s->stream), e3 = cudaStreamSynchronize(s->down);
         if (rc != MASK_OK) return rc;
         MASK_CUDA_TRY(e1);
         MASK_CUDA_TRY(e2);
         MASK_CUDA_TRY(e3);
+        rc = session_kernel_status(s);
+        if (rc != MASK_OK) return rc;
         if (kernel_ms) {
             for (int i = 0; i < chunks; i++) {
                 float ms = 0.f;
@@ -251,14 +280,22 @@ extern "C" int mask_session_spmm_host(mask_session* s, const float* h_B, float* 
         }
         return MASK_OK;
     }
-    MASK_CUDA_TRY(cudaMemcpyAsync(s->d_B, h_B, bb, cudaMemcpyHostToDevice, s->stream));
-    MASK_CUDA_TRY(cudaEventRecord(s->ev0, s->stream));
-    rc = mask_spmm_srbcrs(s->plan, s->d_soff, s->d_sidx, s->d_blk, s->M, s->K, N, s->d_B, N, s->d_C, N, s->d_scratch,
-                          s->scratch_bytes, MASK_EPILOGUE_NONE, s->stream);
+    auto enqueue = [&]() -> int {
+        MASK_CUDA_TRY(cudaMemcpyAsync(s->d_B, h_B, bb, cudaMemcpyHostToDevice, s->stream));
+        MASK_CUDA_TRY(cudaEventRecord(s->ev0, s->stream));
+        int r = mask_spmm_srbcrs(s->plan, s->d_soff, s->d_sidx, s->d_blk, s->M, s->K, N, s->d_B, N, s->d_C, N, s->d_scratch,
+                                 s->scratch_bytes, MASK_EPILOGUE_NONE, s->stream);
+        if (r != MASK_OK) return r;
+        MASK_CUDA_TRY(cudaEventRecord(s->ev1, s->stream));
+        MASK_CUDA_TRY(cudaMemcpyAsync(h_C, s->d_C, cb, cudaMemcpyDeviceToHost, s->stream));
+        return MASK_OK;
+    };
+    rc = enqueue();
+    cudaError_t es = cudaStreamSynchronize(s->stream);   // also after a failed enqueue: the upload may be in flight
     if (rc != MASK_OK) return rc;
-    MASK_CUDA_TRY(cudaEventRecord(s->ev1, s->stream));
-    MASK_CUDA_TRY(cudaMemcpyAsync(h_C, s->d_C, cb, cudaMemcpyDeviceToHost, s->stream));
-    MASK_CUDA_TRY(cudaStreamSynchronize(s->stream));
+    MASK_CUDA_TRY(es);
+    rc = session_kernel_status(s);
+    if (rc != MASK_OK) return rc;
     if (kernel_ms) MASK_CUDA_TRY(cudaEventElapsedTime(kernel_ms, s->ev0, s->ev1));
     return MASK_OK;
 }

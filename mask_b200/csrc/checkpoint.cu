@@ -25,6 +25,39 @@ extern "C" int mask_metcf_checkpoint_name(const char* matrix_name, int32_t M, in
     return MASK_OK;
 }
 
+// The name the reference's testbed gives the file for a matrix read from `file_path` -- the file
+// name without directories and without its last extension -- or, when the path is empty (a matrix
+// generated in memory), "synthetic" plus a sparsity token: the sparsity printed with four decimals,
+// trailing zeros and a trailing point dropped, the point written as 'p'
+// (examples/src_fp32/dtc/testbed/main.cu:171-176, 205-230).
+extern "C" int mask_metcf_checkpoint_name_for(const char* file_path, int32_t M, int32_t K, float sparsity, char* out,
+                                              size_t out_len) {
+    using namespace mask;
+    MASK_REQUIRE(out != nullptr && out_len > 0, "bad arguments");
+    std::string path = file_path ? file_path : "";
+    std::string base = path;
+    const size_t slash = base.find_last_of('/');
+    if (slash != std::string::npos) base = base.substr(slash + 1);
+    const size_t dot = base.find_last_of('.');
+    if (dot != std::string::npos && dot > 0 && base != "..") base = base.substr(0, dot);
+    if (base.empty()) base = "synthetic";
+    std::string name = base + "_M" + std::to_string(M) + "_K" + std::to_string(K) + "_TBK8_RWM16";
+    if (path.empty()) {
+        char buf[64];
+        std::snprintf(buf, sizeof(buf), "%.4f", (double)sparsity);
+        std::string tok = buf;
+        while (!tok.empty() && tok.back() == '0') tok.pop_back();
+        if (!tok.empty() && tok.back() == '.') tok.pop_back();
+        for (char& c : tok)
+            if (c == '.') c = 'p';
+        name += "_sp" + (tok.empty() ? std::string("unknown") : tok);
+    }
+    name += "_METCF.checkpoint";
+    if (name.size() + 1 > out_len) return fail(MASK_ERR_INVALID_ARGUMENT, "name buffer too small");
+    std::memcpy(out, name.c_str(), name.size() + 1);
+    return MASK_OK;
+}
+
 extern "C" int mask_metcf_checkpoint_write(const char* path, int32_t M, int64_t T, int64_t nnz_pad, const int32_t* val_soff,
                                            const int32_t* val_sidx, const int32_t* val_coo_off, const int32_t* val_coo_idx,
                                            const float* val_coo_val) {

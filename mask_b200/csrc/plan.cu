@@ -62,8 +62,12 @@ static void multi_bind(const int32_t* soff, int32_t W, std::vector<int32_t>& tas
 }
 
 static int32_t default_group_tiles(int64_t T) {
-    // enough groups to fill every SM several times over, large enough to amortise a block's
-    // pipeline fill and to keep the number of split-window partial tiles small
+    // The SpMM grid is resident (two blocks per SM) and deals groups round-robin, so the blocks that
+    // run at the same time work on neighbouring groups.  Groups are kept SHORT on purpose: what the
+    // resident blocks touch together is then a narrow band of windows, and rows of B shared by
+    // neighbouring windows (stencils, banded matrices) are fetched from DRAM once and found in L2
+    // by the other blocks.  Groups of 800 tiles measured twice as slow as groups of 128 on a
+    // 27-point stencil and on a power-law graph for exactly that reason.
     const int64_t slots = (int64_t)sm_count() * 3;
     const int64_t g = T / (slots * 4);
     return (int32_t)std::max<int64_t>(8, std::min<int64_t>(128, g));
@@ -111,20 +115,16 @@ static void build_tables(mask_plan& p, const int32_t* soff) {
         }
         if (go.back() != (int32_t)fw.size()) go.push_back((int32_t)fw.size());
     } else {
-        // Windows are cut only when they exceed a group AND the matrix is large enough for the cut
-        // to matter: with fewer than a couple of groups per resident block, a window of up to 128
-        // tiles finishes within the single wave anyway and splitting it would only add the
-        // partial-tile round trip and the fix-up launch.
-        // When it does matter (many groups per block slot) the pieces are made twice as large as
-        // a group of small windows: every piece costs a partial-tile round trip through scratch,
-        // and halving their number was worth 8 % on a 2^20-node power-law graph, while whole
-        // windows pack best into the smaller groups (stencil: 128-tile groups 20 % faster than 256).
-        const int64_t per_slot = p.T / std::max<int64_t>(1, (int64_t)sm_count() * 3);
-        const int32_t split_above = std::max<int32_t>(2 * G, (int32_t)std::min<int64_t>(2 * per_slot, 128));
-        int32_t load = 0, in_group = 0;
+        // Groups are closed on window boundaries once their cost (tiles plus a fixed share per window
+        // for the rows of C it writes) reaches G; a window of more than 5/4 G tiles is cut into
+        // near-equal pieces of at most G tiles, one group each (each piece costs one partial tile in
+        // scratch and the fix-up pass sums them in tile order).
+        constexpr int32_t kWindowCost = 4;
+        const int32_t split_above = G + G / 4;
+        int32_t load = 0;
         auto close = [&]() {
             if (go.back() != (int32_t)fw.size()) go.push_back((int32_t)fw.size());
-            load = 0; in_group = 0;
+            load = 0;
         };
         for (int32_t w = 0; w < W; w++) {
             const int32_t s = soff[w], x = soff[w + 1] - s;
@@ -132,9 +132,9 @@ static void build_tables(mask_plan& p, const int32_t* soff) {
                 fo.push_back(s); fw.push_back(w); close();
                 continue;
             }
-            if (x > split_above) {  // split into near-equal parts, one block each
+            if (x > split_above) {  // split into near-equal parts, one group each
                 close();
-                const int32_t parts = (x + split_above - 1) / split_above, base = x / parts, rem = x % parts;
+                const int32_t parts = (x + G - 1) / G, base = x / parts, rem = x % parts;
                 int32_t at = s;
                 for (int32_t i = 0; i < parts; i++) {
                     fo.push_back(at); fw.push_back(w); close();
@@ -142,9 +142,10 @@ static void build_tables(mask_plan& p, const int32_t* soff) {
                 }
                 continue;
             }
-            if (load + x > G || in_group == kMaxFragsPerGroup) close();
+            if (load > 0 && load + x + kWindowCost > G + G / 8) close();
             fo.push_back(s); fw.push_back(w);
-            load += x; in_group++;
+            load += x + kWindowCost;
+            if (load >= G) close();
         }
         close();
     }
@@ -165,6 +166,8 @@ static void build_tables(mask_plan& p, const int32_t* soff) {
     }
     p.H = (int64_t)p.h_head_frag.size();
     p.max_group_tiles = 0;
+    p.h_group_tile.resize((size_t)p.G + 1);
+    for (int64_t g = 0; g <= p.G; g++) p.h_group_tile[(size_t)g] = fo[go[g]];
     for (int64_t g = 0; g < p.G; g++)
         p.max_group_tiles = std::max<int32_t>(p.max_group_tiles, fo[go[g + 1]] - fo[go[g]]);
 }
@@ -246,6 +249,7 @@ extern "C" int mask_plan_create(const int32_t* d_val_soff, int32_t M, int64_t T,
     if (rc == MASK_OK) rc = upload(p->h_frag_slot, &p->d_frag_slot, st);
     if (rc == MASK_OK) rc = upload(p->h_group_off, &p->d_group_off, st);
     if (rc == MASK_OK) rc = upload(p->h_head_frag, &p->d_head_frag, st);
+    if (rc == MASK_OK) rc = upload(p->h_group_tile, &p->d_group_tile, st);
     if (rc == MASK_OK) rc = upload(std::vector<int32_t>(4, 0), &p->d_status, st);
     if (rc == MASK_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = fail(MASK_ERR_CUDA, "plan upload failed");
     if (rc != MASK_OK) {
@@ -263,6 +267,7 @@ extern "C" void mask_plan_destroy(mask_plan* p) {
     cudaFree(p->d_frag_slot);
     cudaFree(p->d_group_off);
     cudaFree(p->d_head_frag);
+    cudaFree(p->d_group_tile);
     cudaFree(p->d_status);
     delete p;
 }
@@ -304,6 +309,7 @@ extern "C" int mask_plan_status(const mask_plan* p, int32_t* h_status, void* str
     MASK_REQUIRE(p != nullptr && h_status != nullptr, "NULL argument");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     MASK_CUDA_TRY(cudaMemcpyAsync(h_status, p->d_status, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+    MASK_CUDA_TRY(cudaMemsetAsync(p->d_status, 0, sizeof(int32_t), st));   // one expiry must not mark every later call
     MASK_CUDA_TRY(cudaStreamSynchronize(st));
     return MASK_OK;
 }

@@ -23,12 +23,14 @@ struct mask_plan {
     int64_t P = 0;  // fragments that are part of a split window
     int64_t H = 0;  // split windows
     int32_t max_group_tiles = 0;  // most tiles any thread block gets
-    std::vector<int32_t> h_frag_off, h_frag_win, h_frag_slot, h_group_off, h_head_frag;
+    int32_t nslab = 0;  // persistent kernel: 128-column slabs per column block (0 = the widest N fills)
+    std::vector<int32_t> h_frag_off, h_frag_win, h_frag_slot, h_group_off, h_head_frag, h_group_tile;
     int32_t* d_frag_off = nullptr;
     int32_t* d_frag_win = nullptr;
     int32_t* d_frag_slot = nullptr;
     int32_t* d_group_off = nullptr;
     int32_t* d_head_frag = nullptr;
+    int32_t* d_group_tile = nullptr;  // first tile of every group, then T
     const int32_t* d_row_map = nullptr;  // optional, not owned: output row of packed row i (a row reorder's order[])
     float* const* d_peer_out = nullptr;  // optional, not owned: device array of n_peer_out extra output bases
     int32_t n_peer_out = 0;

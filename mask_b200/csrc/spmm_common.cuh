@@ -11,6 +11,10 @@ struct SpmmArgs {
     const int32_t* frag_win;
     const int32_t* frag_slot;
     const int32_t* group_off;
+    const int32_t* group_tile;  // first tile of every group (+ closing entry): persistent kernel only
+    int64_t n_frag;             // fragments in the plan (frag_off has n_frag + 1 entries)
+    int32_t n_groups;
+    int32_t n_col_blocks;       // persistent kernel: column blocks of 128*NSLAB columns
     const int32_t* val_sidx;
     const float* val_blk;      // SR-BCRS
     const int32_t* coo_off;    // ME-TCF: [begin, end) pairs per tile (+ closing entry); MCO: val_mco_off[T+1]
@@ -146,6 +150,10 @@ __device__ __forceinline__ void flush_fragment(const SpmmArgs& p, int ff, int co
 // kUmmaMaxGroupTiles tiles).
 constexpr int kUmmaMaxGroupTiles = 256;
 int launch_spmm_umma(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int variant);
+
+// spmm_sweep.cu: persistent tcgen05 kernel, any N % 4 == 0, groups of any length.  nslab = 128-column
+// slabs per column block (1, 2, 4; 0 = by N); stream_c = streaming stores of C.
+int launch_spmm_sweep(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int nslab, bool stream_c);
 
 // spmm_async.cu: shared-memory ring variant (SR-BCRS).  nq / stages 0 = defaults.
 int launch_spmm_async(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int nq, int stages);

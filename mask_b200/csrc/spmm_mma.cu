@@ -44,6 +44,9 @@ static int g_tune_hints = 0;
 extern int g_session_chunk_cols;      // api.cu: column chunks of the host-buffer pipeline
 static int g_tune_umma_variant = 0;   // 0 = slabs by N, 1 / 2 = 128-column slabs with 4 / 2 tiles per step
 static int g_tune_umma = 1;    // 1 = tcgen05 kernel where it applies (see launch_spmm), 2 = whenever N % 128 == 0
+static int g_tune_sweep = 1;   // 1 = persistent tcgen05 kernel (spmm_sweep.cu) for every product but the compensated ones
+static int g_tune_nslab = 0;   // persistent kernel: 128-column slabs per column block (0 = the plan's choice)
+static int g_tune_stream_c = 0;
 
 template <int NQ, int FMT, int MIN_BLOCKS>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, MIN_BLOCKS) spmm_mma_kernel(const SpmmArgs p) {
@@ -328,6 +331,11 @@ static int launch_spmm(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
         if (rc != MASK_OK) return rc;
         return launch_fixup(plan, a, st);
     }
+    if (g_tune_sweep != 0) {
+        int rc = launch_spmm_sweep(plan, a, st, g_tune_nslab != 0 ? g_tune_nslab : plan->nslab, g_tune_stream_c != 0);
+        if (rc != MASK_OK) return rc;
+        return launch_fixup(plan, a, st);
+    }
     if (umma_fits && (g_tune_umma == 2 || (g_tune_umma == 1 && (METCF || N % 512 == 0)))) {
         int rc = launch_spmm_umma(plan, a, st, g_tune_umma_variant);
         if (rc != MASK_OK) return rc;
@@ -381,6 +389,25 @@ static int check_common(const mask_plan* plan, int32_t M, int32_t K, int32_t N, 
 
 }  // namespace mask
 
+extern "C" int mask_kernel_revision(void) { return 2; }
+
+extern "C" int mask_spmm_kernel_name(const mask_plan* plan, int format, int32_t N, int epilogue, char* out, size_t capacity) {
+    using namespace mask;
+    MASK_REQUIRE(plan != nullptr && out != nullptr && capacity > 0, "NULL argument");
+    MASK_REQUIRE(format >= kFmtSrbcrs && format <= kFmtMco && N > 0, "bad format or N");
+    static const char* const fmt_name[] = {"srbcrs", "metcf", "mco"};
+    if (format == kFmtSrbcrs && (epilogue & MASK_NUMERICS_TF32X3)) {
+        snprintf(out, capacity, "spmm_async_kernel<tf32x3>");
+    } else if (g_tune_sweep != 0) {
+        int nslab = g_tune_nslab != 0 ? g_tune_nslab : plan->nslab;
+        if (nslab != 1 && nslab != 2 && nslab != 4) nslab = N > 256 ? 4 : (N > 128 ? 2 : 1);
+        snprintf(out, capacity, "spmm_sweep_kernel<nslab=%d,%s>", nslab, fmt_name[format]);
+    } else {
+        snprintf(out, capacity, "legacy routing (mask_tune sweep=0), %s", fmt_name[format]);
+    }
+    return MASK_OK;
+}
+
 extern "C" int mask_tune(const char* name, int value) {
     using namespace mask;
     MASK_REQUIRE(name != nullptr, "name is NULL");
@@ -391,6 +418,9 @@ extern "C" int mask_tune(const char* name, int value) {
     else if (!strcmp(name, "hints")) g_tune_hints = value;
     else if (!strcmp(name, "umma")) g_tune_umma = value;
     else if (!strcmp(name, "umma_variant")) g_tune_umma_variant = value;
+    else if (!strcmp(name, "sweep")) g_tune_sweep = value;
+    else if (!strcmp(name, "nslab")) g_tune_nslab = value;
+    else if (!strcmp(name, "stream_c")) g_tune_stream_c = value;
     else if (!strcmp(name, "session_chunk")) g_session_chunk_cols = value;
     else return fail(MASK_ERR_INVALID_ARGUMENT, "unknown tuning knob");
     return MASK_OK;

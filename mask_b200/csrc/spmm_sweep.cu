@@ -1,0 +1,479 @@
+// Persistent tcgen05 SpMM: one resident grid sweeps the matrix once per block of 128*NSLAB columns.
+//
+// The product is issued transposed, as in spmm_umma.cu: for every tile t and 128-column slab,
+//     D^T[128 columns x 16 rows] += Bg^T[128 x 8] * Atile^T[8 x 16]      (tcgen05.mma kind::tf32)
+// with the 8 gathered rows of B as the MN-major operand (128-byte swizzle, 32-byte base) and the
+// stored 16x8 tile as the K-major SWIZZLE_32B operand, accumulators in tensor memory.
+//
+// What differs is who does what, when:
+//   * The grid is resident (blocks per SM x SMs) and every block walks work items
+//     item -> (column block cb = item / G, tile group g = item % G) in item order b, b + grid, ...
+//     Column blocks are the slow index, so the whole GPU works on the same 128*NSLAB columns of B at
+//     about the same time: a row of B then competes for L2 with 512*NSLAB bytes instead of 4N, which is
+//     what cuts the re-fetching of rows on power-law matrices (NSLAB = 1 or 2), while matrices whose
+//     gathers already hit in L2 take the whole width at once (NSLAB = 4 at N = 512: tile values and
+//     column ids are read once).  Odd column blocks walk the groups backwards, so the tile values
+//     that are still in L2 at the end of one sweep are the first ones the next sweep wants.
+//   * A pipeline step is always 4 units of 8 rows x 128 columns (16 KB of gathered rows): the NSLAB
+//     slabs of KT = 4 / NSLAB consecutive tiles.  Steps run through the tiles of a group without
+//     regard to window boundaries; only the MMA issuer and the epilogue know about windows.
+//   * The block lives for the whole launch: barriers, tensor memory and the pipeline are set up
+//     once, not once per group, and groups can be as long as the planner likes.
+//   * Column ids are not staged in shared memory: a producer warp loads the ids of a step with one
+//     coalesced load four steps ahead and hands them out with shuffles.
+//   * Any N % 4 == 0: units are filled only where the column exists and the epilogue stores only
+//     such columns (tensor-memory lanes of missing columns hold garbage that is never read).
+//
+// Roles (352 threads): warps 0-3 epilogue (tensor-memory lanes 32w..32w+31 = columns of a slab),
+// warp 4 issues the MMAs (one lane), warps 5-6 prepare alternate steps (round the tile values to
+// TF32 / expand ME-TCF and MCO tiles, then fence.proxy.async: cp.async writes through the generic
+// proxy), warps 7-10 produce.  Rings: full[s] (producers -> prepare), ready[s] (prepare -> MMA),
+// empty[s] (tcgen05.commit -> producers), acc_full / acc_empty[NACC] (accumulator buffers of
+// 16*NSLAB tensor-memory columns, so the epilogue of a window overlaps the MMAs of the next ones).
+//
+// Every wait is bounded (about a second of SM clock).  On expiry the block raises its abort flag and
+// the plan's device status word; every role leaves its loops, the producers wait for their copies,
+// the MMA lane commits to a drain barrier and waits (bounded) until the tensor core has finished
+// with shared and tensor memory, and only then is tensor memory freed.
+#include "spmm_common.cuh"
+#include "umma_ptx.cuh"
+
+namespace mask {
+
+constexpr int kSweepThreads = 352;
+
+template <int NSLAB, int FMT>
+struct SweepLayout {
+    static constexpr int KT = 4 / NSLAB;                            // tiles per step
+    static constexpr int S = FMT == kFmtSrbcrs ? 6 : 5;             // ring stages
+    static constexpr int kStageB = 4 * 4096;                        // gathered rows of one step
+    static constexpr int kStageA = KT * 512;                        // tile operand(s) of one step
+    // staging per tile: ME-TCF 32 idx + 32 val of the run, then [begin, end); MCO 16 B of mask, up to
+    // 128 values, then [begin, end) of the values
+    static constexpr int kCooStride = FMT == kFmtMco ? 544 : (FMT == kFmtMetcf ? 272 : 0);
+    static constexpr int kRunAt = FMT == kFmtMco ? 528 : 256;       // where [begin, end) sits in a tile's staging
+    static constexpr int kNacc = NSLAB == 4 ? 4 : 8;                // accumulator buffers
+    static constexpr int kAccCols = 16 * NSLAB;
+    static constexpr int kTmemCols = kNacc * kAccCols;              // 256, 256, 128: two blocks fit an SM's 512
+    static constexpr int kB = 0;
+    static constexpr int kA = S * kStageB;
+    static constexpr int kCoo = kA + S * kStageA;
+    static constexpr int kBars = kCoo + ((S * KT * kCooStride + 15) & ~15);   // full[S], empty[S], ready[S], acc_full[NACC], acc_empty[NACC], drain
+    static constexpr int kNumBars = 3 * S + 2 * kNacc + 1;
+    static constexpr int kTmemSlot = kBars + kNumBars * 8;
+    static constexpr int kAbort = kTmemSlot + 8;
+    static constexpr int kBytes = kAbort + 8;
+    static constexpr int kDynamicBytes = kBytes + 1024;             // room to align the base to 1024 B
+    static_assert(kTmemCols == 128 || kTmemCols == 256, "tensor-memory allocations are powers of two");
+};
+
+// A wait that only the clock bounds: used once, at teardown, when the abort flag may already be up.
+__device__ __forceinline__ bool mbar_wait_drain(uint32_t bar, uint32_t parity) {
+    const long long start = clock64();
+    while (!mbar_test(bar, parity)) {
+        if (clock64() - start > kUmmaWaitCycles) return false;
+    }
+    return true;
+}
+
+template <int NSLAB, int FMT, bool STREAM_C>
+__global__ void __launch_bounds__(kSweepThreads, 2) spmm_sweep_kernel(const SpmmArgs p, int32_t* status) {
+    constexpr bool METCF = FMT == kFmtMetcf, MCO = FMT == kFmtMco;
+    using L = SweepLayout<NSLAB, FMT>;
+    constexpr int KT = L::KT, S = L::S, NACC = L::kNacc, kAccCols = L::kAccCols;
+    constexpr int kLook = 4;                                        // steps the column ids are loaded ahead
+    extern __shared__ unsigned char sweep_smem_raw[];
+    const uint32_t raw = (uint32_t)__cvta_generic_to_shared(sweep_smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;                   // swizzle patterns are functions of the address bits
+    unsigned char* gbase = sweep_smem_raw + (base - raw);
+    const uint32_t bars = base + L::kBars;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (S + s); };
+    auto ready_bar = [&](int s) { return bars + 8u * (2 * S + s); };
+    auto accf_bar = [&](int b) { return bars + 8u * (3 * S + b); };
+    auto acce_bar = [&](int b) { return bars + 8u * (3 * S + NACC + b); };
+    const uint32_t drain_bar = bars + 8u * (3 * S + 2 * NACC);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + L::kAbort);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + L::kTmemSlot);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = p.n_groups;
+    const int n_items = p.n_col_blocks * G;
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < S; s++) {
+            mbar_init(full_bar(s), 128);   // one deferred arrive per producer thread
+            mbar_init(empty_bar(s), 1);    // tcgen05.commit
+            mbar_init(ready_bar(s), 1);    // lane 0 of the preparing warp
+        }
+        for (int b = 0; b < NACC; b++) {
+            mbar_init(accf_bar(b), 1);     // tcgen05.commit
+            mbar_init(acce_bar(b), 4);     // lane 0 of every epilogue warp
+        }
+        mbar_init(drain_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(base + L::kTmemSlot),
+                     "r"(L::kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    // item -> (column block, group): column blocks slowest, odd ones walk the groups backwards
+    auto item_cb = [&](int item) { return item / G; };
+    auto item_group = [&](int item, int cb) {
+        const int gi = item - cb * G;
+        return (cb & 1) ? G - 1 - gi : gi;
+    };
+
+    if (warp >= 7) {
+        // ------------------------------ producers ------------------------------------------------
+        const int pw = warp - 7;                 // this warp copies 32-column atom pw of every unit
+        const int lr = lane >> 3, lc = lane & 7; // row (and row + 4), 16-byte chunk
+        const uint32_t off0 = (uint32_t)(pw * 1024 + lr * 128 + ((lc ^ (2 * lr)) * 16));   // 32-byte chunks swizzled by row % 4
+        const uint32_t ldb_bytes = (uint32_t)(p.ldb * 4);
+        const int idl = lane & (8 * KT - 1);     // which of the step's 8*KT ids this lane loads
+        int s = 0;
+        uint32_t round = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            const int cb = item_cb(item);
+            const int g = item_group(item, cb);
+            const int t0 = p.group_tile[g], t1 = p.group_tile[g + 1];
+            const int colt = cb * (128 * NSLAB) + 32 * pw + 4 * lc;   // this thread's column in slab 0
+            const char* Bcol = reinterpret_cast<const char*>(p.B + colt);
+            bool valid[NSLAB];
+#pragma unroll
+            for (int sl = 0; sl < NSLAB; sl++) valid[sl] = colt + 128 * sl < p.N;
+            auto load_ids = [&](int tb) -> int {
+                const int64_t at = (int64_t)tb * kTileCols + idl;
+                return at < (int64_t)t1 * kTileCols ? __ldg(p.val_sidx + at) : 0;
+            };
+            // ME-TCF / MCO: [begin, end) of the value run of tile tb + lane, loaded ahead like the ids
+            auto load_run = [&](int tb) -> int2 {
+                int2 r = make_int2(0, 0);
+                if (FMT != kFmtSrbcrs) {
+                    const int64_t tile = (int64_t)tb + lane;
+                    if (lane < KT && tile < t1) {
+                        if (METCF) r = __ldg(reinterpret_cast<const int2*>(p.coo_off) + tile);
+                        else r = make_int2(__ldg(p.coo_off + tile), __ldg(p.coo_off + tile + 1));
+                    }
+                }
+                return r;
+            };
+            int q0 = load_ids(t0), q1 = load_ids(t0 + KT), q2 = load_ids(t0 + 2 * KT), q3 = load_ids(t0 + 3 * KT);
+            int2 r0q = load_run(t0), r1q = load_run(t0 + KT), r2q = load_run(t0 + 2 * KT), r3q = load_run(t0 + 3 * KT);
+            static_assert(kLook == 4, "the queues below are four deep");
+            for (int tb = t0; tb < t1; tb += KT) {
+                const int cnt = min(KT, t1 - tb);
+                const int cur = q0;
+                const int2 rcur = r0q;
+                q0 = q1; q1 = q2; q2 = q3;
+                r0q = r1q; r1q = r2q; r2q = r3q;
+                q3 = load_ids(tb + kLook * KT);
+                r3q = load_run(tb + kLook * KT);
+                // the verdict of a wait is made warp-uniform: the shuffles below need every lane
+                if (round > 0 && !__all_sync(0xffffffffu, mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag))) { ok = false; break; }
+                const uint32_t dst = base + L::kB + s * L::kStageB + off0;
+#pragma unroll
+                for (int u = 0; u < KT; u++) {
+                    const int id0 = __shfl_sync(0xffffffffu, cur, u * kTileCols + lr);
+                    const int id1 = __shfl_sync(0xffffffffu, cur, u * kTileCols + lr + 4);
+                    if (u < cnt) {
+                        const char* r0 = Bcol + (uint64_t)(uint32_t)id0 * ldb_bytes;
+                        const char* r1 = Bcol + (uint64_t)(uint32_t)id1 * ldb_bytes;
+#pragma unroll
+                        for (int sl = 0; sl < NSLAB; sl++) {
+                            if (valid[sl]) {
+                                cp16(dst + (u * NSLAB + sl) * 4096, r0 + sl * 512);
+                                cp16(dst + (u * NSLAB + sl) * 4096 + 512, r1 + sl * 512);
+                            }
+                        }
+                    }
+                }
+                // tile operand(s): warp u copies the one of tile u of the step
+                int2 run = make_int2(0, 0);
+                if (FMT != kFmtSrbcrs) run = make_int2(__shfl_sync(0xffffffffu, rcur.x, pw), __shfl_sync(0xffffffffu, rcur.y, pw));
+                if (pw < cnt) {
+                    const int64_t tile = tb + pw;
+                    if (METCF) {
+                        // [begin, end) of the run, then its first 32 entries (runs start on multiples of 8
+                        // entries and are padded to 8)
+                        const uint32_t st = base + L::kCoo + (s * KT + pw) * L::kCooStride;
+                        if (lane == 16)
+                            asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(st + L::kRunAt), "l"(p.coo_off + 2 * tile) : "memory");
+                        const int chunk = lane & 7;   // 4 entries
+                        if (lane < 16 && run.x + 4 * chunk < ((run.y + 7) & ~7)) {
+                            const void* src = lane < 8 ? static_cast<const void*>(p.coo_idx + run.x + 4 * chunk)
+                                                       : static_cast<const void*>(p.coo_val + run.x + 4 * chunk);
+                            cp16(st + lane * 16, src);
+                        }
+                    } else if (MCO) {
+                        const uint32_t st = base + L::kCoo + (s * KT + pw) * L::kCooStride;
+                        const int o0 = run.x, o1 = run.y;
+                        if (lane == 0) cp16(st, p.mco_mask + 2 * tile);
+                        if (lane < 2)
+                            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(st + L::kRunAt + 4 * lane), "l"(p.coo_off + tile + lane) : "memory");
+                        if (o0 + 4 * lane < o1) cp16(st + 16 + lane * 16, p.coo_val + o0 + 4 * lane);   // runs are multiples of 4 values
+                    } else {
+                        cp16(base + L::kA + s * L::kStageA + pw * 512 + lane * 16, p.val_blk + tile * kTileElems + lane * 4);
+                    }
+                }
+                // arrives on full[s] once every copy this thread has issued so far has landed
+                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(full_bar(s)) : "memory");
+                if (++s == S) { s = 0; round++; }
+            }
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+    } else if (warp >= 5) {
+        // ------------------------------ prepare (two warps, alternate steps) -------------------------
+        const int q = warp - 5;
+        int s = 0;
+        uint32_t round = 0, step = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            const int g = item_group(item, item_cb(item));
+            const int t0 = p.group_tile[g], t1 = p.group_tile[g + 1];
+            for (int tb = t0; tb < t1; tb += KT, step++) {
+                const int cnt = min(KT, t1 - tb);
+                if ((step & 1) == (uint32_t)q) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(full_bar(s), round & 1, abort_flag))) { ok = false; break; }
+#pragma unroll
+                    for (int u = 0; u < KT; u++) {
+                        if (u < cnt) {
+                            unsigned char* aslot = gbase + L::kA + s * L::kStageA + u * 512;
+                            if (METCF) {  // rebuild the 16x8 operand: zero, then tile[idx] = rna(value) over the run
+                                const unsigned char* st = gbase + L::kCoo + (s * KT + u) * L::kCooStride;
+                                uint32_t* tile = reinterpret_cast<uint32_t*>(aslot);
+                                reinterpret_cast<uint4*>(tile)[lane] = make_uint4(0u, 0u, 0u, 0u);
+                                __syncwarp();
+                                const int2 run = *reinterpret_cast<const int2*>(st + L::kRunAt);
+                                const int rcnt = run.y - run.x;
+                                const int* sidx = reinterpret_cast<const int*>(st);
+                                const uint32_t* sval = reinterpret_cast<const uint32_t*>(st + 128);
+                                if (lane < rcnt) tile[sidx[lane]] = sval[lane] + 0x1000u;
+                                for (int e = run.x + 32 + lane; e < run.y; e += 32)   // dense tiles: entries beyond the staged 32
+                                    tile[__ldg(p.coo_idx + e)] = __float_as_uint(__ldg(p.coo_val + e)) + 0x1000u;
+                                __syncwarp();
+                            } else if (MCO) {
+                                const unsigned char* st = gbase + L::kCoo + (s * KT + u) * L::kCooStride;
+                                const ulonglong2 m = *reinterpret_cast<const ulonglong2*>(st);
+                                reinterpret_cast<uint4*>(aslot)[lane] = mco_expand(m.x, m.y, reinterpret_cast<const uint32_t*>(st + 16), lane);
+                            } else {  // round the tile values to TF32 (nearest, ties away) in place
+                                uint4* at = reinterpret_cast<uint4*>(aslot) + lane;
+                                uint4 v = *at;
+                                v.x += 0x1000u; v.y += 0x1000u; v.z += 0x1000u; v.w += 0x1000u;
+                                *at = v;
+                            }
+                        }
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(ready_bar(s));
+                }
+                if (++s == S) { s = 0; round++; }
+            }
+        }
+    } else if (warp == 4) {
+        // ------------------------------ MMA issuer (one lane) ------------------------------------------
+        if (lane == 0) {
+            int s = 0;
+            uint32_t round = 0, acc_it = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+                const int g = item_group(item, item_cb(item));
+                int f = p.group_off[g];
+                const int t1 = p.group_tile[g + 1];
+                int t = p.group_tile[g];
+                int f_end_tile = p.frag_off[f + 1];                               // end of fragment f
+                int f_next_end = p.frag_off[min((int64_t)f + 2, p.n_frag)];      // end of fragment f + 1, loaded ahead
+                bool open = false;                                                // the fragment has MMAs in flight
+                uint32_t buf = 0;
+                while (t < t1) {
+                    const int cnt = min(KT, t1 - t);
+                    if (!mbar_wait(ready_bar(s), round & 1, abort_flag)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                    for (int u = 0; u < KT; u++) {
+                        if (u < cnt && ok) {
+                            while (t >= f_end_tile) {   // on to the fragment that holds tile t (fragments without tiles are skipped)
+                                if (open) { umma_commit(accf_bar(buf)); acc_it++; open = false; }
+                                f++;
+                                f_end_tile = f_next_end;
+                                f_next_end = p.frag_off[min((int64_t)f + 2, p.n_frag)];
+                            }
+                            if (!open) {
+                                buf = acc_it % NACC;
+                                if (acc_it >= (uint32_t)NACC && !mbar_wait(acce_bar(buf), (acc_it / NACC - 1) & 1, abort_flag)) ok = false;
+                                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                            }
+                            if (ok) {
+                                const uint64_t bdesc = umma_smem_desc(base + L::kA + s * L::kStageA + u * 512, 1, 16, kSwizzle32B);
+#pragma unroll
+                                for (int sl = 0; sl < NSLAB; sl++) {
+                                    const uint64_t adesc = umma_smem_desc(base + L::kB + s * L::kStageB + (u * NSLAB + sl) * 4096, 64, 32, kSwizzle128B32B);
+                                    umma_tf32(tmem_base + buf * kAccCols + sl * 16, adesc, bdesc, open ? 1u : 0u);
+                                }
+                                open = true;
+                                t++;
+                            }
+                        }
+                    }
+                    if (!ok) break;
+                    umma_commit(empty_bar(s));   // the slot is free once these MMAs have read it
+                    if (++s == S) { s = 0; round++; }
+                }
+                if (open) { umma_commit(accf_bar(buf)); acc_it++; }
+            }
+            // whatever was issued must have finished before shared and tensor memory go away
+            umma_commit(drain_bar);
+            if (!mbar_wait_drain(drain_bar, 0)) *abort_flag = 1;
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------ epilogue -------------------------------------------------
+        uint32_t acc_it = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            const int cb = item_cb(item);
+            const int g = item_group(item, cb);
+            const int col = cb * (128 * NSLAB) + 32 * warp + lane;   // + 128 * slab
+            const int f0 = p.group_off[g], f_end = p.group_off[g + 1];
+            // fragment f's tile count, window and slot are loaded one fragment ahead
+            int nxt_n = 0, nxt_w = 0, nxt_slot = -1;
+            if (f0 < f_end) {
+                nxt_n = p.frag_off[f0 + 1] - p.frag_off[f0];
+                nxt_w = p.frag_win[f0];
+                nxt_slot = p.frag_slot[f0];
+            }
+            for (int f = f0; f < f_end; f++) {
+                const int n = nxt_n, w = nxt_w, slot = nxt_slot;
+                if (f + 1 < f_end) {
+                    nxt_n = p.frag_off[f + 2] - p.frag_off[f + 1];
+                    nxt_w = p.frag_win[f + 1];
+                    nxt_slot = p.frag_slot[f + 1];
+                }
+                const int rows_ok = slot < 0 ? p.M - w * kWinRows : kWinRows;
+                const bool relu = p.relu && slot < 0;
+                uint32_t v[NSLAB][16];
+                if (n == 0) {
+#pragma unroll
+                    for (int sl = 0; sl < NSLAB; sl++)
+#pragma unroll
+                        for (int i = 0; i < 16; i++) v[sl][i] = 0u;
+                } else {
+                    const uint32_t buf = acc_it % NACC;
+                    if (!__all_sync(0xffffffffu, mbar_wait(accf_bar(buf), (acc_it / NACC) & 1, abort_flag))) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t taddr = tmem_base + ((uint32_t)(32 * warp) << 16) + buf * kAccCols;
+#pragma unroll
+                    for (int sl = 0; sl < NSLAB; sl++) tmem_ld16(taddr + sl * 16, v[sl]);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(acce_bar(buf));   // the MMA warp may reuse this buffer
+                    acc_it++;
+                }
+                if (relu) {
+#pragma unroll
+                    for (int sl = 0; sl < NSLAB; sl++)
+#pragma unroll
+                        for (int i = 0; i < 16; i++) v[sl][i] = __float_as_uint(fmaxf(__uint_as_float(v[sl][i]), 0.f));
+                }
+                bool colok[NSLAB];
+#pragma unroll
+                for (int sl = 0; sl < NSLAB; sl++) colok[sl] = col + 128 * sl < p.N;
+                // destination 0 is C (or the partial-tile scratch); 1.. are the peers' copies of C, which
+                // get the finished rows with plain stores over NVLink
+                const int n_dst = slot < 0 ? 1 + p.n_peer_out : 1;
+#pragma unroll 1
+                for (int d = 0; d < n_dst; d++) {
+                    float* cb_ptr = slot >= 0 ? p.scratch + (int64_t)slot * kWinRows * p.N : (d == 0 ? p.C : p.peer_out[d - 1]);
+                    int row0 = w * kWinRows;
+                    asm volatile("" : "+r"(row0));   // keeps the 16 row offsets from being hoisted out of this loop into registers
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const int r = FMT != kFmtSrbcrs ? i : (i ^ (i >> 3));   // MMA-N index -> window row (SR-BCRS: rows 8..15 swapped pairwise)
+                        if (r < rows_ok) {
+                            const int64_t off = slot >= 0 ? (int64_t)r * p.N
+                                                          : (int64_t)(p.row_map ? p.row_map[row0 + r] : row0 + r) * p.ldc;
+#pragma unroll
+                            for (int sl = 0; sl < NSLAB; sl++) {
+                                if (colok[sl]) {
+                                    if (STREAM_C && slot < 0 && d == 0) __stcs(cb_ptr + off + col + 128 * sl, __uint_as_float(v[sl][i]));
+                                    else cb_ptr[off + col + 128 * sl] = __uint_as_float(v[sl][i]);
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- teardown: everybody gets here, aborting or not ---------------------------------------------
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 4) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::kTmemCols) : "memory");
+    }
+    if (tid == 0 && *abort_flag) atomicExch(status, 1);
+}
+
+template <int NSLAB, int FMT, bool STREAM_C>
+static int launch_sweep_variant(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
+    using L = SweepLayout<NSLAB, FMT>;
+    static_assert(2 * (L::kDynamicBytes + 1024) <= 228 * 1024, "two blocks per SM");
+    auto kern = spmm_sweep_kernel<NSLAB, FMT, STREAM_C>;
+    MASK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));   // per device
+    static int blocks_per_sm = 0;   // per instantiation; the same on every device this library runs on
+    if (blocks_per_sm == 0) {
+        int n = 0;
+        MASK_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kSweepThreads, L::kDynamicBytes));
+        if (n < 1) return fail(MASK_ERR_CUDA, "the tcgen05 kernel does not fit on this device");
+        blocks_per_sm = n > 2 ? 2 : n;   // tensor memory: at most 256 columns per block, 512 per SM
+    }
+    a.n_col_blocks = (a.N + 128 * NSLAB - 1) / (128 * NSLAB);
+    const int64_t items = (int64_t)a.n_col_blocks * plan->G;
+    if (items >= ((int64_t)1 << 31)) return fail(MASK_ERR_INVALID_ARGUMENT, "too many work items");
+    const int64_t resident = (int64_t)blocks_per_sm * sm_count();
+    const unsigned grid = (unsigned)(items < resident ? items : resident);
+    kern<<<grid, kSweepThreads, L::kDynamicBytes, st>>>(a, plan->d_status);
+    MASK_CUDA_TRY(cudaGetLastError());
+    return MASK_OK;
+}
+
+template <int FMT>
+static int launch_sweep_fmt(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int nslab, bool stream_c) {
+    if (stream_c) {
+        if (nslab == 1) return launch_sweep_variant<1, FMT, true>(plan, a, st);
+        if (nslab == 2) return launch_sweep_variant<2, FMT, true>(plan, a, st);
+        return launch_sweep_variant<4, FMT, true>(plan, a, st);
+    }
+    if (nslab == 1) return launch_sweep_variant<1, FMT, false>(plan, a, st);
+    if (nslab == 2) return launch_sweep_variant<2, FMT, false>(plan, a, st);
+    return launch_sweep_variant<4, FMT, false>(plan, a, st);
+}
+
+// nslab: 128-column slabs per column block (1, 2 or 4); 0 = the widest that N fills.
+int launch_spmm_sweep(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int nslab, bool stream_c) {
+    if (a.N % 4 != 0) return fail(MASK_ERR_INVALID_ARGUMENT, "N must be a multiple of 4");
+    if (plan->d_group_tile == nullptr) return fail(MASK_ERR_INVALID_ARGUMENT, "plan has no group tile table");
+    if (nslab != 1 && nslab != 2 && nslab != 4) nslab = a.N > 256 ? 4 : (a.N > 128 ? 2 : 1);
+    SpmmArgs b = a;
+    b.group_tile = plan->d_group_tile;
+    b.n_groups = (int32_t)plan->G;
+    b.n_frag = plan->F;
+    if (a.mco_mask) return launch_sweep_fmt<kFmtMco>(plan, b, st, nslab, stream_c);
+    if (a.coo_off) return launch_sweep_fmt<kFmtMetcf>(plan, b, st, nslab, stream_c);
+    return launch_sweep_fmt<kFmtSrbcrs>(plan, b, st, nslab, stream_c);
+}
+
+}  // namespace mask

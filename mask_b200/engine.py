@@ -319,5 +319,13 @@ def spmm(packed, dense: torch.Tensor, out: torch.Tensor | None = None, policy: s
     return out
 
 
+def kernel_signature(packed, N: int, plan: Plan, tf32x3: bool = False) -> tuple[str, int]:
+    """(name of the kernel ``spmm`` launches for this matrix, plan and N; the library's kernel revision)."""
+    fmt = 2 if isinstance(packed, PackedMCO) else (1 if isinstance(packed, PackedMETCF) else 0)
+    buf = C.create_string_buffer(128)
+    check(lib().mask_spmm_kernel_name(plan._h, fmt, N, _lib.NUMERICS_TF32X3 if tf32x3 else 0, buf, 128), "mask_spmm_kernel_name")
+    return buf.value.decode(), int(lib().mask_kernel_revision())
+
+
 def tune(name: str, value: int) -> None:
     check(lib().mask_tune(name.encode(), value), "mask_tune")

@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import torch
 
-from _common import Cache, check_input, engine, fill_side_outputs, run
+from _common import Cache, check_input, engine, fill_side_outputs, pack_without_sync, run
 
 _cache = Cache()
 
@@ -28,8 +28,8 @@ def _preprocess(colind, rowptr, num_nodes, blk_h, blk_w, block_partition, edge_t
     if int(blk_h) != 16 or int(blk_w) != 8:
         raise RuntimeError(f"ME-TCF uses 16x8 tiles: got blk_h={blk_h} blk_w={blk_w}")
     num_nodes = int(num_nodes)
-    K = max(num_nodes, int(colind.max().item()) + 1) if colind.numel() else num_nodes
-    packed = engine.pack_metcf(rowptr, colind, values, num_nodes, K)
+    packed = pack_without_sync(engine.pack_metcf, rowptr, colind, num_nodes, values)
+    K = packed.K
     # side outputs come from the SR-BCRS fill of the same analysis (tiles per window, condensed
     # column and row of every entry)
     ones = values if values is not None else torch.ones(colind.numel(), dtype=torch.float32, device=colind.device)

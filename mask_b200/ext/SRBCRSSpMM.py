@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import torch
 
-from _common import Cache, check_input, engine, fill_side_outputs, run
+from _common import Cache, check_input, engine, fill_side_outputs, pack_without_sync, run
 
 _cache = Cache()
 _BASE_MSG = ("the 32x32 SR-BCRS variant is not built in this library: select the 16x8 variant "
@@ -33,8 +33,8 @@ def _preprocess(colind, rowptr, values, num_nodes, blk_h, blk_w, block_partition
     if values.numel() != colind.numel():
         raise RuntimeError("values length must equal colind length")
     num_nodes = int(num_nodes)
-    K = max(num_nodes, int(colind.max().item()) + 1) if colind.numel() else num_nodes
-    packed = engine.pack_srbcrs(rowptr, colind, values, num_nodes, K, side_outputs=True)
+    packed = pack_without_sync(lambda rp, ci, va, M, K: engine.pack_srbcrs(rp, ci, va, M, K, side_outputs=True),
+                               rowptr, colind, num_nodes, values)
     fill_side_outputs((packed.block_partition, packed.edge_to_col, packed.edge_to_row), block_partition, edge_to_col,
                       edge_to_row)
     dev = rowptr.device

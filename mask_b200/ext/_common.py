@@ -61,12 +61,31 @@ def fill_side_outputs(packed_or_maps, block_partition, edge_to_col, edge_to_row)
         edge_to_row[: e2r.numel()].copy_(e2r)
 
 
+def pack_without_sync(pack, rowptr, colind, num_nodes, *more):
+    """Packs with K = num_nodes (a graph adjacency: the common case, no extra device round trip)
+    and only when the packer reports a column beyond that asks the device for the largest one."""
+    from mask_b200 import _lib
+    try:
+        return pack(rowptr, colind, *more, num_nodes, num_nodes)
+    except _lib.MaskError as e:
+        if e.status != 6 or not colind.numel():   # MASK_ERR_COLUMN_RANGE
+            raise
+    K = int(colind.max().item()) + 1
+    return pack(rowptr, colind, *more, num_nodes, K)
+
+
 def run(cache, dense, row_window_offset, num_nodes, policy_override=None):
-    check_input(dense, "dense", torch.float32)
+    if not isinstance(dense, torch.Tensor) or not dense.is_cuda or dense.dtype != torch.float32:
+        raise RuntimeError("dense must be a float32 CUDA tensor")
     check_input(row_window_offset, "row_window_offset")
     packed, policy = cache.get(row_window_offset)
     if dense.dim() != 2:
         raise RuntimeError("dense must be 2-D")
+    # like the reference extension: any layout (made contiguous here) and any number of rows that
+    # covers the matrix's columns (examples/src_fp32/sr_bcrs/testbed/SRBCRSSpMM_kernel.cu:404-406)
+    if dense.size(0) < packed.K:
+        raise RuntimeError(f"dense has {dense.size(0)} rows but the matrix references column {packed.K - 1}")
+    dense = dense[: packed.K].contiguous()
     if int(num_nodes) != packed.M:
         raise RuntimeError(f"num_nodes mismatch: preprocess saw {packed.M}, run got {num_nodes}")
     if dense.size(1) == 0:

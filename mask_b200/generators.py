@@ -5,14 +5,35 @@ row-sharded sweep, GCN adjacency).
 The reference project evaluates on 26 SuiteSparse / GNN matrices that are not distributed with
 it (``dataset/matrices.tar.gz`` is a git-LFS pointer); these generators stand in for them.  All
 matrices come back as CSR with int32 indices, rows sorted strictly ascending (deduplicated),
-float32 values -- the input contract of the packers.  Everything is NumPy on the host and fully
-determined by the seed, so every rank of a multi-GPU run can rebuild the same matrix.
+float32 values -- the input contract of the packers.  Every random draw is NumPy on the host and
+the result is fully determined by the seed, so every rank of a multi-GPU run gets the same matrix.
+The heavy integer passes of the large R-MAT graphs (bit assembly, sort + deduplication, the value
+hash) run on the GPU when one is visible -- they are exact, so the matrix is bit-identical either
+way -- and ``make_workload_cached`` keeps finished matrices in a temporary directory so that the
+ranks of one job, and the jobs that follow on the same machine, build each matrix once.
 """
 from __future__ import annotations
 
+import os
+import tempfile
+import time
 from dataclasses import dataclass
 
 import numpy as np
+
+
+GPU_MIN_ITEMS = 1 << 22   # below this many samples / entries the host does everything
+
+
+def _cuda(items: int = 1 << 62):
+    """torch, if a CUDA device can take the exact integer passes of the big generators."""
+    if items < GPU_MIN_ITEMS:
+        return None
+    try:
+        import torch
+        return torch if torch.cuda.is_available() else None
+    except Exception:
+        return None
 
 
 @dataclass
@@ -37,8 +58,13 @@ class CSR:
 
 
 def _csr_from_sorted_keys(keys: np.ndarray, n: int, k: int) -> tuple[np.ndarray, np.ndarray]:
-    rows = keys // k
-    colind = (keys - rows * k).astype(np.int32)
+    if k & (k - 1) == 0:
+        sh = k.bit_length() - 1
+        rows = keys >> sh
+        colind = (keys & (k - 1)).astype(np.int32)
+    else:
+        rows = keys // k
+        colind = (keys - rows * k).astype(np.int32)
     counts = np.bincount(rows, minlength=n)
     rowptr = np.zeros(n + 1, dtype=np.int64)
     np.cumsum(counts, out=rowptr[1:])
@@ -68,12 +94,24 @@ def uniform_random(n: int = 4096, density: float = 0.005, seed: int = 101) -> CS
     return CSR(n, n, rowptr, colind, values)
 
 
-def _rmat_edges(scale: int, n_samples: int, seed: int, a=0.57, b=0.19, c=0.19) -> tuple[np.ndarray, np.ndarray]:
-    """R-MAT: one quadrant draw per bit, no noise.  Returns int64 (src, dst) samples."""
+def _rmat_edges(scale: int, n_samples: int, seed: int, a=0.57, b=0.19, c=0.19):
+    """R-MAT: one quadrant draw per bit, no noise.  Returns int64 (src, dst) samples (NumPy arrays,
+    or CUDA tensors when a GPU does the bit assembly)."""
     rng = np.random.Generator(np.random.PCG64(seed))
+    ab, abc = np.float32(a + b), np.float32(a + b + c)
+    torch = _cuda(n_samples)
+    if torch is not None:
+        src = torch.zeros(n_samples, dtype=torch.int64, device="cuda")
+        dst = torch.zeros(n_samples, dtype=torch.int64, device="cuda")
+        for _ in range(scale):
+            r = torch.from_numpy(rng.random(n_samples, dtype=np.float32)).cuda()
+            row_bit = r >= float(ab)
+            col_bit = ((r >= float(np.float32(a))) & (r < float(ab))) | (r >= float(abc))
+            src = (src << 1) | row_bit
+            dst = (dst << 1) | col_bit
+        return src, dst
     src = np.zeros(n_samples, dtype=np.int64)
     dst = np.zeros(n_samples, dtype=np.int64)
-    ab, abc = np.float32(a + b), np.float32(a + b + c)
     for _ in range(scale):
         r = rng.random(n_samples, dtype=np.float32)
         row_bit = r >= ab
@@ -84,8 +122,21 @@ def _rmat_edges(scale: int, n_samples: int, seed: int, a=0.57, b=0.19, c=0.19) -
 
 
 def _symmetric_rmat_keys(scale: int, samples_per_node: int, seed: int, self_loops: bool) -> np.ndarray:
+    """Sorted, deduplicated keys row * n + col of the symmetrised sample set."""
     n = 1 << scale
     src, dst = _rmat_edges(scale, samples_per_node * n, seed)
+    if not isinstance(src, np.ndarray):   # CUDA tensors: sort + deduplicate there
+        import torch
+        parts = [src * n + dst, dst * n + src]
+        del src, dst
+        if self_loops:
+            parts.append(torch.arange(n, dtype=torch.int64, device="cuda") * (n + 1))
+        keys = torch.unique(torch.cat(parts))
+        del parts
+        out = keys.cpu().numpy()
+        del keys
+        torch.cuda.empty_cache()
+        return out
     parts = [src * n + dst, dst * n + src]
     if self_loops:
         parts.append(np.arange(n, dtype=np.int64) * (n + 1))
@@ -109,8 +160,27 @@ def rmat_symmetric_uniform(scale: int = 22, samples_per_node: int = 16, seed: in
     n = 1 << scale
     keys = _symmetric_rmat_keys(scale, samples_per_node, seed, self_loops=False)
     rowptr, colind = _csr_from_sorted_keys(keys, n, n)
-    rows = keys // n
-    cols = keys - rows * n
+    torch = _cuda(keys.shape[0])
+    if torch is not None:   # the same 64-bit hash in two's-complement int64 (logical shifts by masking)
+        k = torch.from_numpy(keys).cuda()
+        rows = k >> scale
+        cols = k & (n - 1)
+        x = (torch.minimum(rows, cols) * n + torch.maximum(rows, cols)) ^ seed
+        del k, rows, cols
+
+        def i64(v):
+            return v - (1 << 64) if v >= (1 << 63) else v
+
+        x = x + i64(0x9E3779B97F4A7C15)
+        x = (x ^ ((x >> 30) & ((1 << 34) - 1))) * i64(0xBF58476D1CE4E5B9)
+        x = (x ^ ((x >> 27) & ((1 << 37) - 1))) * i64(0x94D049BB133111EB)
+        x = x ^ ((x >> 31) & ((1 << 33) - 1))
+        values = (((x >> 40) & ((1 << 24) - 1)).to(torch.float64) / float(1 << 24) * 2.0 - 1.0).to(torch.float32).cpu().numpy()
+        del x
+        torch.cuda.empty_cache()
+        return CSR(n, n, rowptr, colind, values)
+    rows = keys >> scale
+    cols = keys & (n - 1)
     canon = (np.minimum(rows, cols) * n + np.maximum(rows, cols)).astype(np.uint64)
     h = _splitmix64(canon ^ np.uint64(seed))
     values = ((h >> np.uint64(40)).astype(np.float64) / float(1 << 24) * 2.0 - 1.0).astype(np.float32)
@@ -152,6 +222,25 @@ def dense_normal(rows: int, cols: int, seed: int) -> np.ndarray:
     return rng.standard_normal((rows, cols), dtype=np.float32)
 
 
+def dense_normal_blocks(rows: int, cols: int, seed: int, threads: int, block_rows: int = 1 << 16) -> np.ndarray:
+    """N(0,1) float32 like ``dense_normal`` but drawn by ``threads`` workers, every block of rows
+    from its own PCG64 stream spawned from the seed (so the values differ from ``dense_normal``'s
+    single stream).  For operands of several GiB where only the distribution matters."""
+    from concurrent.futures import ThreadPoolExecutor
+    out = np.empty((rows, cols), dtype=np.float32)
+    starts = list(range(0, rows, block_rows))
+    seqs = np.random.SeedSequence(seed).spawn(len(starts))
+
+    def fill(i):
+        r0 = starts[i]
+        r1 = min(rows, r0 + block_rows)
+        np.random.Generator(np.random.PCG64(seqs[i])).standard_normal((r1 - r0, cols), dtype=np.float32, out=out[r0:r1])
+
+    with ThreadPoolExecutor(max_workers=max(1, threads)) as ex:
+        list(ex.map(fill, range(len(starts))))
+    return out
+
+
 def glorot_uniform(fan_in: int, fan_out: int, seed: int) -> np.ndarray:
     rng = np.random.Generator(np.random.PCG64(seed))
     lim = float(np.sqrt(6.0 / (fan_in + fan_out)))
@@ -175,6 +264,50 @@ def make_workload(name: str, **overrides) -> tuple[CSR, int]:
     kw = dict(kwargs)
     kw.update(overrides)
     return builder(**kw), bseed
+
+
+def make_workload_cached(name: str, cache_dir: str | None = None, wait_s: float = 900.0, **overrides) -> tuple[CSR, int]:
+    """``make_workload`` through a file cache (``$MASK_B200_CACHE`` or a folder in the system's
+    temporary directory): the first caller builds and saves the matrix, concurrent callers (the
+    other ranks of a job) wait for the file, later callers load it."""
+    builder, kwargs, bseed = WORKLOADS[name]
+    kw = dict(kwargs)
+    kw.update(overrides)
+    root = cache_dir or os.environ.get("MASK_B200_CACHE") or os.path.join(tempfile.gettempdir(), "mask_b200_workloads")
+    os.makedirs(root, exist_ok=True)
+    tag = name + "".join(f"_{k}{v}" for k, v in sorted(kw.items())) + "_v1"
+    path, lock = os.path.join(root, tag + ".npz"), os.path.join(root, tag + ".lock")
+
+    def load():
+        z = np.load(path)
+        return CSR(int(z["M"]), int(z["K"]), z["rowptr"], z["colind"], z["values"]), bseed
+
+    if os.path.exists(path):
+        return load()
+    try:
+        fd = os.open(lock, os.O_CREAT | os.O_EXCL | os.O_WRONLY)
+        os.close(fd)
+        mine = True
+    except FileExistsError:
+        mine = False
+    if not mine:   # somebody else is building it
+        t0 = time.time()
+        while time.time() - t0 < wait_s:
+            if os.path.exists(path):
+                return load()
+            time.sleep(0.5)
+        return builder(**kw), bseed   # a stale lock: build without the cache
+    try:
+        m = builder(**kw)
+        tmp = path + f".{os.getpid()}.tmp.npz"
+        np.savez(tmp, M=m.M, K=m.K, rowptr=m.rowptr, colind=m.colind, values=m.values)
+        os.replace(tmp, path)
+    finally:
+        try:
+            os.remove(lock)
+        except OSError:
+            pass
+    return m, bseed
 
 
 def check_csr(csr: CSR) -> None:

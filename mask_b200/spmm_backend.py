@@ -29,6 +29,18 @@ def reset_backend_state() -> None:
     _cache.clear()
 
 
+def _pack_square_first(pack, rp, ci, va, num_rows):
+    """Packs with K = num_rows (graph adjacency, no device round trip for the column count) and asks
+    the device for the largest column only when the packer reports one beyond that."""
+    from ._lib import MaskError
+    try:
+        return pack(rp, ci, va, num_rows, num_rows)
+    except MaskError as e:
+        if e.status != 6 or not ci.numel():   # MASK_ERR_COLUMN_RANGE
+            raise
+    return pack(rp, ci, va, num_rows, int(ci.max().item()) + 1)
+
+
 def _prep(fmt, rowptr, colind, values, num_rows, variant):
     key = (fmt, variant, int(rowptr.data_ptr()), int(colind.data_ptr()), int(values.data_ptr()) if values is not None else 0,
            int(num_rows), int(colind.numel()))
@@ -37,12 +49,13 @@ def _prep(fmt, rowptr, colind, values, num_rows, variant):
         rp = rowptr if rowptr.dtype == torch.int32 else rowptr.to(torch.int32)
         ci = colind if colind.dtype == torch.int32 else colind.to(torch.int32)
         va = None if values is None else (values if values.dtype == torch.float32 else values.to(torch.float32))
-        K = max(int(num_rows), int(ci.max().item()) + 1) if ci.numel() else int(num_rows)
+        rp, ci = rp.contiguous(), ci.contiguous()
         if fmt == "sr_bcrs":
-            packed = engine.pack_srbcrs(rp.contiguous(), ci.contiguous(), va.contiguous(), int(num_rows), K)
+            if va is None:   # pattern-only graph: unit weights
+                va = torch.ones(ci.numel(), dtype=torch.float32, device=ci.device)
+            packed = _pack_square_first(engine.pack_srbcrs, rp, ci, va.contiguous(), int(num_rows))
         else:
-            packed = engine.pack_metcf(rp.contiguous(), ci.contiguous(), None if va is None else va.contiguous(),
-                                       int(num_rows), K)
+            packed = _pack_square_first(engine.pack_metcf, rp, ci, None if va is None else va.contiguous(), int(num_rows))
         hit = (packed, (rowptr, colind, values))  # keep the CSR alive: the key holds its addresses
         _cache[key] = hit
     return hit[0]

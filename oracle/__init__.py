@@ -287,6 +287,19 @@ def spmm_abs_f64(M, rowptr, colind, values, B, rows=None):
     return Cm
 
 
+def spmm_rows(rowptr, colind, values, B, rows):
+    """Reference product and |A|.|B| restricted to a list of rows: (C[rows], (|A|.|B|)[rows])."""
+    rows = np.asarray(rows, dtype=np.int64)
+    rp = np.asarray(rowptr).astype(np.int64)
+    lens = rp[rows + 1] - rp[rows]
+    ptr = np.zeros(rows.size + 1, dtype=np.int64)
+    np.cumsum(lens, out=ptr[1:])
+    idx = np.repeat(rp[rows] - ptr[:-1], lens) + np.arange(int(ptr[-1]), dtype=np.int64)
+    cols, vals = np.ascontiguousarray(colind[idx]), np.ascontiguousarray(values[idx])
+    ptr32 = ptr.astype(np.int32)
+    return spmm_f32(rows.size, ptr32, cols, vals, B), spmm_abs_f64(rows.size, ptr32, cols, vals, B)
+
+
 def spmm_from_srbcrs(M, packed, B, round_tf32=True):
     L = lib()
     B = _c(B, np.float32)
@@ -383,6 +396,17 @@ def ref_metcf_checkpoint_roundtrip(cache_dir, matrix_name, M, K, rowptr, colind,
     if R.ref_metcf_store_checkpoint(fake_path, M, K) != 1:
         raise RuntimeError("reference storeCheckpoint failed")
     return os.path.join(cache_dir, f"{matrix_name}_M{M}_K{K}_TBK8_RWM16_METCF.checkpoint"), packed
+
+
+def ref_metcf_checkpoint_stem(file_path: str, M: int, K: int, sparsity: float) -> str:
+    """The reference's own buildCheckpointStem."""
+    R = _ref("libref_metcf.so")
+    R.ref_metcf_checkpoint_stem.restype = C.c_int
+    R.ref_metcf_checkpoint_stem.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_float, C.c_char_p, C.c_int]
+    buf = C.create_string_buffer(512)
+    if R.ref_metcf_checkpoint_stem(file_path.encode(), M, K, sparsity, buf, 512) != 1:
+        raise RuntimeError("name too long")
+    return buf.value.decode()
 
 
 def ref_metcf_load_checkpoint(cache_dir, matrix_name, M, K):

@@ -10,7 +10,7 @@ import os
 import sys
 from pathlib import Path
 
-ref = Path(os.environ.get("MASK_REF", "/root/reference"))
+ref = Path(os.environ["MASK_REF"])   # the checkout must be named: there is no default location
 sys.path.insert(0, str(ref / "python"))
 sys.path.insert(0, str(ref / "python" / "test"))
 here = Path(__file__).resolve().parent

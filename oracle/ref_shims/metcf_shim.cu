@@ -61,4 +61,12 @@ int ref_metcf_load_checkpoint(const char* matrix_file_path, int M, int K, int* T
     return ok;
 }
 
+// The file name the reference derives from a matrix path and sparsity (main.cu:205-230).
+int ref_metcf_checkpoint_stem(const char* matrix_file_path, int M, int K, float sparsity, char* out, int out_len) {
+    const std::string stem = buildCheckpointStem(std::string(matrix_file_path), M, K, sparsity);
+    if ((int)stem.size() + 1 > out_len) return 0;
+    std::memcpy(out, stem.c_str(), stem.size() + 1);
+    return 1;
+}
+
 }  // extern "C"

@@ -8,7 +8,7 @@ import json
 import os
 import sys
 
-ref = os.environ.get("MASK_REF", "/root/reference")
+ref = os.environ["MASK_REF"]   # the checkout must be named: there is no default location
 sys.path.insert(0, os.path.join(ref, "python"))
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 

@@ -146,6 +146,26 @@ def _read_checkpoint(L, path, M, K):
     return rc, out
 
 
+@pytest.mark.parametrize("path,M,K,sp,want", [
+    ("/data/sets/web-Google.mtx", 916428, 916428, 0.0, "web-Google_M916428_K916428_TBK8_RWM16_METCF.checkpoint"),
+    ("cage.tar.mtx", 5, 7, 0.5, "cage.tar_M5_K7_TBK8_RWM16_METCF.checkpoint"),
+    ("", 100, 200, 0.9995, "synthetic_M100_K200_TBK8_RWM16_sp0p9995_METCF.checkpoint"),
+    ("", 100, 200, 0.5, "synthetic_M100_K200_TBK8_RWM16_sp0p5_METCF.checkpoint"),
+    ("", 16, 16, 1.0, "synthetic_M16_K16_TBK8_RWM16_sp1_METCF.checkpoint"),
+    ("", 16, 16, 0.99999, "synthetic_M16_K16_TBK8_RWM16_sp1_METCF.checkpoint"),
+])
+def test_metcf_checkpoint_name_follows_the_reference(oracle_mod, path, M, K, sp, want):
+    """The cache file must be found by the reference binary too: same name from the same path,
+    including the sparsity token it appends for matrices generated in memory."""
+    L = _lib.lib()
+    buf = C.create_string_buffer(256)
+    assert L.mask_metcf_checkpoint_name_for(path.encode(), M, K, sp, buf, 256) == 0
+    assert buf.value.decode() == want
+    if oracle_mod.ref_available():
+        assert oracle_mod.ref_metcf_checkpoint_stem(path, M, K, sp) == want
+    assert L.mask_metcf_checkpoint_name_for(path.encode(), M, K, sp, buf, 8) == 1
+
+
 @pytest.mark.parametrize("name", ["rmat10", "m17", "hub_rows"])
 def test_metcf_checkpoint_file(oracle_mod, tmp_path, name):
     """Write / read round trip, validation on load, and byte compatibility with the reference's own

@@ -147,3 +147,37 @@ def test_caller_level_callables(oracle_mod):
     assert len(spmm_backend._cache) > 0 and n_cached >= 2
     spmm_backend.reset_backend_state()
     assert not spmm_backend._cache
+
+
+@pytest.mark.gpu
+def test_dense_operand_layouts_like_the_reference(oracle_mod):
+    """The reference extension makes `dense` contiguous itself and does not care how many rows it
+    has beyond the matrix's columns; pattern-only graphs (values=None) multiply with unit weights."""
+    import torch
+    from mask_b200 import spmm_backend
+    sr = _mod("SRBCRSSpMM")
+    m = cases.SMALL["rmat10"]()
+    rp, ci, va = _dev(m)
+    W = (m.M + 15) // 16
+    bp = torch.zeros(W, dtype=torch.int32, device="cuda")
+    e2c = torch.zeros(m.nnz, dtype=torch.int32, device="cuda")
+    e2r = torch.zeros(m.nnz, dtype=torch.int32, device="cuda")
+    rwo, _, tile_id, tc_off, a2x, _ = sr.preprocess_gpu_16x8(ci, rp, va, m.M, 16, 8, bp, e2c, e2r)
+    B = np.random.Generator(np.random.PCG64(15)).standard_normal((m.K + 40, 64), dtype=np.float32)
+    ref = oracle_mod.spmm_f32(m.M, m.rowptr, m.colind, m.values, B[: m.K])
+    absp = oracle_mod.spmm_abs_f64(m.M, m.rowptr, m.colind, m.values, B[: m.K])
+    tall = torch.from_numpy(B).cuda()                                   # more rows than columns of A
+    strided = torch.from_numpy(np.ascontiguousarray(B.T)).cuda().t()    # column-major storage
+    assert not strided.is_contiguous()
+    for d in (tall, strided):
+        out = sr.run_SRBCRS_16x8(d, rwo, tile_id, tc_off, a2x, m.M, m.nnz, "")[0]
+        assert oracle_mod.check_tolerance(out.cpu().numpy(), ref, absp)[0] == 0
+    with pytest.raises(RuntimeError, match="rows"):
+        sr.run_SRBCRS_16x8(tall[: m.K - 1], rwo, tile_id, tc_off, a2x, m.M, m.nnz, "")
+    spmm_backend.reset_backend_state()
+    ones = np.ones_like(m.values)
+    out = spmm_backend.srbcrs_spmm(rp, ci, None, tall[: m.K], m.M, 64, m.M)
+    ref1 = oracle_mod.spmm_f32(m.M, m.rowptr, m.colind, ones, B[: m.K])
+    absp1 = oracle_mod.spmm_abs_f64(m.M, m.rowptr, m.colind, ones, B[: m.K])
+    assert oracle_mod.check_tolerance(out.cpu().numpy(), ref1, absp1)[0] == 0
+    spmm_backend.reset_backend_state()

@@ -181,3 +181,17 @@ def test_reordered_pack_and_product(oracle_mod, name, kind):
         assert bad == 0, worst
     with pytest.raises(RuntimeError):
         engine.spmm(p, torch.zeros((m.K, 16), device="cuda"), plan=engine.Plan(p.val_soff, m.M, p.T))
+
+
+def test_generators_gpu_passes_are_exact(monkeypatch):
+    """The large R-MAT workloads do their integer passes (bit assembly, sort + deduplication, value
+    hash) on the GPU when one is there; the matrix must be bit-identical to the host-only path."""
+    from mask_b200 import generators as G
+    got = {}
+    for where, floor in (("gpu", 0), ("host", 1 << 62)):
+        monkeypatch.setattr(G, "GPU_MIN_ITEMS", floor)
+        got[where] = (G.rmat_symmetric_uniform(scale=13, samples_per_node=16, seed=401),
+                      G.rmat_gcn_normalised(scale=13, samples_per_node=8, seed=201))
+    for a, b in zip(got["gpu"], got["host"]):
+        assert a.M == b.M and np.array_equal(a.rowptr, b.rowptr) and np.array_equal(a.colind, b.colind)
+        assert np.array_equal(a.values.view(np.int32), b.values.view(np.int32))

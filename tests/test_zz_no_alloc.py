@@ -58,6 +58,60 @@ def test_static_scratch_matches_caller_scratch(oracle_mod, name, N, group_tiles)
     assert bad == 0, worst
 
 
+def _one_wide_window(K):
+    """16 rows that together hold K distinct columns: one window of K / 8 tiles."""
+    from mask_b200 import generators as G
+    per_row = K // 16
+    rowptr = (np.arange(17) * per_row).astype(np.int32)
+    colind = np.arange(16 * per_row, dtype=np.int32)
+    rng = np.random.Generator(np.random.PCG64(3))
+    return G.CSR(16, K, rowptr, colind, rng.uniform(-1, 1, size=colind.size).astype(np.float32))
+
+
+def test_static_scratch_allocates_nothing_and_fills_to_the_brim(oracle_mod):
+    """The point of the entry point: a caller whose device heap is spoken for can use it.  After one
+    warm-up call (which looks up the array's address) further calls leave the device's free memory
+    and torch's allocator exactly as they were.  The plan here needs the whole array: 1024 partial
+    tiles at N = 512 is the stated limit, and it must be accepted, not refused."""
+    import torch
+    from mask_b200 import _lib, engine
+    L = _lib.lib()
+    N = 512
+    m = _one_wide_window(8192)   # 1024 tiles in one window; group_tiles = 1 cuts it into 1024 pieces
+    rp, ci, va = (torch.from_numpy(x).cuda() for x in (m.rowptr, m.colind, m.values))
+    p = engine.pack_srbcrs(rp, ci, va, m.M, m.K)
+    plan = engine.Plan(p.val_soff, m.M, p.T, "auto", 1)
+    assert plan.info()["partial"] == 1024 and plan.scratch_bytes(N) == L.mask_static_scratch_capacity()
+    rng = np.random.Generator(np.random.PCG64(78))
+    Bh = rng.standard_normal((m.K, N), dtype=np.float32)
+    B = torch.from_numpy(Bh).cuda()
+    out = torch.full((m.M, N), float("nan"), device="cuda")
+    _lib.check(_call_static(L, plan, p, B, out), "warm-up call")
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    stats0 = (torch.cuda.memory_allocated(), torch.cuda.memory_reserved(), torch.cuda.memory_stats().get("num_alloc_retries", 0),
+              torch.cuda.memory_stats().get("allocation.all.allocated", 0))
+    for _ in range(5):
+        _lib.check(_call_static(L, plan, p, B, out), "mask_spmm_srbcrs_static_scratch")
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    stats1 = (torch.cuda.memory_allocated(), torch.cuda.memory_reserved(), torch.cuda.memory_stats().get("num_alloc_retries", 0),
+              torch.cuda.memory_stats().get("allocation.all.allocated", 0))
+    assert free1 == free0, "the driver's free memory changed: something was allocated or freed"
+    assert stats1 == stats0, "torch's allocator was used"
+    ref = oracle_mod.spmm_f32(m.M, m.rowptr, m.colind, m.values, Bh)
+    absp = oracle_mod.spmm_abs_f64(m.M, m.rowptr, m.colind, m.values, Bh)
+    bad, worst = oracle_mod.check_tolerance(out.cpu().numpy(), ref, absp, RTOL, ATOL)
+    assert bad == 0, worst
+    # one more tile than the array holds is refused
+    m2 = _one_wide_window(8192 + 16 * 8)
+    rp, ci, va = (torch.from_numpy(x).cuda() for x in (m2.rowptr, m2.colind, m2.values))
+    p2 = engine.pack_srbcrs(rp, ci, va, m2.M, m2.K)
+    plan2 = engine.Plan(p2.val_soff, m2.M, p2.T, "auto", 1)
+    assert plan2.info()["partial"] > 1024
+    assert _call_static(L, plan2, p2, torch.zeros((m2.K, N), device="cuda"), out) == 4  # MASK_ERR_SCRATCH_TOO_SMALL
+
+
 def test_static_scratch_refuses_oversized_plans():
     import torch
     from mask_b200 import _lib, engine, generators as G
