@@ -167,27 +167,30 @@ __global__ void __launch_bounds__(kSweepThreads, 2) spmm_sweep_kernel(const Spmm
                 }
                 return r;
             };
-            int q0 = load_ids(t0), q1 = load_ids(t0 + KT), q2 = load_ids(t0 + 2 * KT), q3 = load_ids(t0 + 3 * KT);
-            int2 r0q = load_run(t0), r1q = load_run(t0 + KT), r2q = load_run(t0 + 2 * KT), r3q = load_run(t0 + 3 * KT);
-            static_assert(kLook == 4, "the queues below are four deep");
-            for (int tb = t0; tb < t1; tb += KT) {
+            // One pipeline step.  q / rq hold the ids / value runs of this step (loaded four steps ago);
+            // they are handed out with shuffles first and then REFILLED IN PLACE for the step four ahead, so
+            // a queue register is written by a load and read four steps later and never moved: a move
+            // would wait for the load it carries and put one memory latency into every step.
+            auto produce = [&](int tb, int& q, int2& rq) -> bool {
                 const int cnt = min(KT, t1 - tb);
-                const int cur = q0;
-                const int2 rcur = r0q;
-                q0 = q1; q1 = q2; q2 = q3;
-                r0q = r1q; r1q = r2q; r2q = r3q;
-                q3 = load_ids(tb + kLook * KT);
-                r3q = load_run(tb + kLook * KT);
-                // the verdict of a wait is made warp-uniform: the shuffles below need every lane
-                if (round > 0 && !__all_sync(0xffffffffu, mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag))) { ok = false; break; }
+                int id0[KT], id1[KT];
+#pragma unroll
+                for (int u = 0; u < KT; u++) {
+                    id0[u] = __shfl_sync(0xffffffffu, q, u * kTileCols + lr);
+                    id1[u] = __shfl_sync(0xffffffffu, q, u * kTileCols + lr + 4);
+                }
+                int2 run = make_int2(0, 0);
+                if (FMT != kFmtSrbcrs) run = make_int2(__shfl_sync(0xffffffffu, rq.x, pw), __shfl_sync(0xffffffffu, rq.y, pw));
+                q = load_ids(tb + kLook * KT);
+                rq = load_run(tb + kLook * KT);
+                // the verdict of a wait is made warp-uniform: every lane takes part in the next step's shuffles
+                if (round > 0 && !__all_sync(0xffffffffu, mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag))) return false;
                 const uint32_t dst = base + L::kB + s * L::kStageB + off0;
 #pragma unroll
                 for (int u = 0; u < KT; u++) {
-                    const int id0 = __shfl_sync(0xffffffffu, cur, u * kTileCols + lr);
-                    const int id1 = __shfl_sync(0xffffffffu, cur, u * kTileCols + lr + 4);
                     if (u < cnt) {
-                        const char* r0 = Bcol + (uint64_t)(uint32_t)id0 * ldb_bytes;
-                        const char* r1 = Bcol + (uint64_t)(uint32_t)id1 * ldb_bytes;
+                        const char* r0 = Bcol + (uint64_t)(uint32_t)id0[u] * ldb_bytes;
+                        const char* r1 = Bcol + (uint64_t)(uint32_t)id1[u] * ldb_bytes;
 #pragma unroll
                         for (int sl = 0; sl < NSLAB; sl++) {
                             if (valid[sl]) {
@@ -198,8 +201,6 @@ __global__ void __launch_bounds__(kSweepThreads, 2) spmm_sweep_kernel(const Spmm
                     }
                 }
                 // tile operand(s): warp u copies the one of tile u of the step
-                int2 run = make_int2(0, 0);
-                if (FMT != kFmtSrbcrs) run = make_int2(__shfl_sync(0xffffffffu, rcur.x, pw), __shfl_sync(0xffffffffu, rcur.y, pw));
                 if (pw < cnt) {
                     const int64_t tile = tb + pw;
                     if (METCF) {
@@ -228,6 +229,19 @@ __global__ void __launch_bounds__(kSweepThreads, 2) spmm_sweep_kernel(const Spmm
                 // arrives on full[s] once every copy this thread has issued so far has landed
                 asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(full_bar(s)) : "memory");
                 if (++s == S) { s = 0; round++; }
+                return true;
+            };
+            static_assert(kLook == 4, "the queues below are four deep");
+            int q0 = load_ids(t0), q1 = load_ids(t0 + KT), q2 = load_ids(t0 + 2 * KT), q3 = load_ids(t0 + 3 * KT);
+            int2 r0q = load_run(t0), r1q = load_run(t0 + KT), r2q = load_run(t0 + 2 * KT), r3q = load_run(t0 + 3 * KT);
+            for (int tb = t0; tb < t1; tb += 4 * KT) {
+                if (!produce(tb, q0, r0q)) { ok = false; break; }
+                if (tb + KT >= t1) break;
+                if (!produce(tb + KT, q1, r1q)) { ok = false; break; }
+                if (tb + 2 * KT >= t1) break;
+                if (!produce(tb + 2 * KT, q2, r2q)) { ok = false; break; }
+                if (tb + 3 * KT >= t1) break;
+                if (!produce(tb + 3 * KT, q3, r3q)) { ok = false; break; }
             }
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
@@ -433,13 +447,11 @@ static int launch_sweep_variant(const mask_plan* plan, SpmmArgs a, cudaStream_t 
     static_assert(2 * (L::kDynamicBytes + 1024) <= 228 * 1024, "two blocks per SM");
     auto kern = spmm_sweep_kernel<NSLAB, FMT, STREAM_C>;
     MASK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));   // per device
-    static int blocks_per_sm = 0;   // per instantiation; the same on every device this library runs on
-    if (blocks_per_sm == 0) {
-        int n = 0;
-        MASK_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kSweepThreads, L::kDynamicBytes));
-        if (n < 1) return fail(MASK_ERR_CUDA, "the tcgen05 kernel does not fit on this device");
-        blocks_per_sm = n > 2 ? 2 : n;   // tensor memory: at most 256 columns per block, 512 per SM
-    }
+    MASK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    // Two blocks per SM by construction: shared memory (asserted above), registers (launch bounds) and
+    // tensor memory (at most 256 of the SM's 512 columns per block) all fit twice.  The occupancy
+    // calculator is not asked: it answered 1 here because it assumes the default carveout.
+    constexpr int blocks_per_sm = 2;
     a.n_col_blocks = (a.N + 128 * NSLAB - 1) / (128 * NSLAB);
     const int64_t items = (int64_t)a.n_col_blocks * plan->G;
     if (items >= ((int64_t)1 << 31)) return fail(MASK_ERR_INVALID_ARGUMENT, "too many work items");
