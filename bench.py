@@ -585,7 +585,7 @@ def main():
     pack_ms = (time.perf_counter() - t0) * 1e3
     distinct = int(torch.unique(ci).numel()) if panel.nnz else 0
     del rp, va
-    plan = engine.Plan(packed.val_soff, panel.M, packed.T, args.policy, args.group_tiles)
+    plan = packed.new_plan(args.policy, args.group_tiles)
     info = plan.info()
     out = torch.empty((panel.M, N), dtype=torch.float32, device=dev)
     launches_per_step = 1 + (1 if info["partial"] > 0 else 0)

@@ -243,6 +243,14 @@ int mask_peer_alloc(size_t bytes, void** d_ptr, void* handle);
 int mask_peer_open(const void* handle, void** d_ptr);
 int mask_peer_close(void* d_ptr);
 int mask_peer_free(void* d_ptr);
+/* Prepares the plan for the TMA-fed SpMM kernel: keeps a copy of val_block_val (128 T floats, owned
+ * by the plan) with every value rounded to TF32 -- nearest, ties away, the reference kernels'
+ * cvt.rna (examples/src_fp32/sr_bcrs/testbed/kernel.inc:809-814) done once per matrix instead of
+ * once per use.  mask_spmm_srbcrs then takes its fastest path whenever it is called with the same
+ * val_block_val pointer; with another pointer, or a plan that was not prepared, it runs the
+ * copy-based kernel, which rounds on the fly.  Call it again after changing the values in place;
+ * NULL drops the copy.  Allocates (cudaMalloc) and enqueues one kernel on `stream`. */
+int mask_plan_prepare_values(mask_plan* plan, const float* d_val_block_val, void* stream);
 /* Reads AND CLEARS the plan's device status word (synchronises the stream): 0, or non-zero if a
  * kernel launched with this plan since the last call gave up on one of its bounded waits (its
  * output is then invalid; the kernel has drained its copies and tensor-core work and freed its

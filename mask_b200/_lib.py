@@ -46,6 +46,7 @@ SIGNATURES = {
     "mask_plan_scratch_bytes": (sz, [vp, i32]),
     "mask_plan_info": (C.c_int, [vp, C.POINTER(i64), C.POINTER(i64), C.POINTER(i64), C.POINTER(i32)]),
     "mask_plan_export": (C.c_int, [vp, vp, vp, vp]),
+    "mask_plan_prepare_values": (C.c_int, [vp, vp, vp]),
     "mask_plan_status": (C.c_int, [vp, C.POINTER(i32), vp]),
     "mask_spmm_srbcrs": (C.c_int, [vp, vp, vp, vp, i32, i32, i32, vp, i64, vp, i64, vp, sz, C.c_int, vp]),
     "mask_spmm_metcf": (C.c_int, [vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, i64, vp, i64, vp, sz, C.c_int, vp]),

@@ -167,7 +167,9 @@ extern "C" int mask_session_create_srbcrs(int32_t M, int32_t K, int64_t T, const
             MASK_CUDA_TRY(cudaMemcpyAsync(s->d_sidx, h_val_sidx, (size_t)T * 8 * 4, cudaMemcpyHostToDevice, s->stream));
             MASK_CUDA_TRY(cudaMemcpyAsync(s->d_blk, h_val_block_val, (size_t)T * 128 * 4, cudaMemcpyHostToDevice, s->stream));
         }
-        return mask_plan_create(s->d_soff, M, T, policy, 0, s->stream, &s->plan);
+        rc = mask_plan_create(s->d_soff, M, T, policy, 0, s->stream, &s->plan);
+        if (rc != MASK_OK) return rc;
+        return mask_plan_prepare_values(s->plan, s->d_blk, s->stream);
     };
     int rc = body();
     if (rc != MASK_OK) { mask_session_destroy(s); return rc; }
@@ -211,7 +213,9 @@ extern "C" int mask_session_create_csr(int32_t M, int32_t K, int64_t nnz, const 
         rc = mask_srbcrs_fill(d_rowptr, d_colind, d_values, M, nnz, d_ws, s->d_soff, s->T, s->d_sidx, s->d_blk, nullptr,
                               nullptr, nullptr, s->stream);
         if (rc != MASK_OK) return rc;
-        return mask_plan_create(s->d_soff, M, s->T, policy, 0, s->stream, &s->plan);
+        rc = mask_plan_create(s->d_soff, M, s->T, policy, 0, s->stream, &s->plan);
+        if (rc != MASK_OK) return rc;
+        return mask_plan_prepare_values(s->plan, s->d_blk, s->stream);
     };
     int rc = body();
     if (s->stream) cudaStreamSynchronize(s->stream);

@@ -268,6 +268,7 @@ extern "C" void mask_plan_destroy(mask_plan* p) {
     cudaFree(p->d_group_off);
     cudaFree(p->d_head_frag);
     cudaFree(p->d_group_tile);
+    cudaFree(p->d_vals_tf32);
     cudaFree(p->d_status);
     delete p;
 }

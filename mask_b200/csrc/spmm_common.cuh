@@ -30,6 +30,7 @@ struct SpmmArgs {
     int64_t ldc;
     float* scratch;
     int32_t M;
+    int32_t K;
     int32_t N;
     int32_t relu;
     int32_t tf32x3;  // compensated products (MASK_NUMERICS_TF32X3)
@@ -154,6 +155,11 @@ int launch_spmm_umma(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, 
 // spmm_sweep.cu: persistent tcgen05 kernel, any N % 4 == 0, groups of any length.  nslab = 128-column
 // slabs per column block (1, 2, 4; 0 = by N); stream_c = streaming stores of C.
 int launch_spmm_sweep(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int nslab, bool stream_c);
+
+// spmm_tma.cu: persistent tcgen05 kernel fed by the tensor memory accelerator (SR-BCRS with a prepared
+// plan, see mask_plan_prepare_values).
+bool spmm_tma_applies(const mask_plan* plan, const SpmmArgs& a);
+int launch_spmm_tma(const mask_plan* plan, const SpmmArgs& a, int64_t K, cudaStream_t st, int nslab, bool stream_c);
 
 // spmm_async.cu: shared-memory ring variant (SR-BCRS).  nq / stages 0 = defaults.
 int launch_spmm_async(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int nq, int stages);

@@ -47,6 +47,7 @@ static int g_tune_umma = 1;    // 1 = tcgen05 kernel where it applies (see launc
 static int g_tune_sweep = 1;   // 1 = persistent tcgen05 kernel (spmm_sweep.cu) for every product but the compensated ones
 static int g_tune_nslab = 0;   // persistent kernel: 128-column slabs per column block (0 = the plan's choice)
 static int g_tune_stream_c = 0;
+static int g_tune_tma = 0;     // 1 = the TMA-fed kernel where the plan holds rounded tile values (spmm_tma.cu); measured slower, off by default
 
 template <int NQ, int FMT, int MIN_BLOCKS>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, MIN_BLOCKS) spmm_mma_kernel(const SpmmArgs p) {
@@ -331,6 +332,11 @@ static int launch_spmm(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
         if (rc != MASK_OK) return rc;
         return launch_fixup(plan, a, st);
     }
+    if (g_tune_sweep != 0 && g_tune_tma != 0 && FMT == kFmtSrbcrs && spmm_tma_applies(plan, a)) {
+        int rc = launch_spmm_tma(plan, a, a.K, st, g_tune_nslab != 0 ? g_tune_nslab : plan->nslab, g_tune_stream_c != 0);
+        if (rc != MASK_OK) return rc;
+        return launch_fixup(plan, a, st);
+    }
     if (g_tune_sweep != 0) {
         int rc = launch_spmm_sweep(plan, a, st, g_tune_nslab != 0 ? g_tune_nslab : plan->nslab, g_tune_stream_c != 0);
         if (rc != MASK_OK) return rc;
@@ -401,7 +407,8 @@ extern "C" int mask_spmm_kernel_name(const mask_plan* plan, int format, int32_t 
     } else if (g_tune_sweep != 0) {
         int nslab = g_tune_nslab != 0 ? g_tune_nslab : plan->nslab;
         if (nslab != 1 && nslab != 2 && nslab != 4) nslab = N > 256 ? 4 : (N > 128 ? 2 : 1);
-        snprintf(out, capacity, "spmm_sweep_kernel<nslab=%d,%s>", nslab, fmt_name[format]);
+        const bool tma = g_tune_tma != 0 && format == kFmtSrbcrs && plan->d_vals_tf32 != nullptr;
+        snprintf(out, capacity, "%s<nslab=%d,%s>", tma ? "spmm_tma_kernel" : "spmm_sweep_kernel", nslab, fmt_name[format]);
     } else {
         snprintf(out, capacity, "legacy routing (mask_tune sweep=0), %s", fmt_name[format]);
     }
@@ -421,6 +428,7 @@ extern "C" int mask_tune(const char* name, int value) {
     else if (!strcmp(name, "sweep")) g_tune_sweep = value;
     else if (!strcmp(name, "nslab")) g_tune_nslab = value;
     else if (!strcmp(name, "stream_c")) g_tune_stream_c = value;
+    else if (!strcmp(name, "tma")) g_tune_tma = value;
     else if (!strcmp(name, "session_chunk")) g_session_chunk_cols = value;
     else return fail(MASK_ERR_INVALID_ARGUMENT, "unknown tuning knob");
     return MASK_OK;
@@ -440,7 +448,7 @@ extern "C" int mask_spmm_srbcrs(const mask_plan* plan, const int32_t* d_val_soff
     a.val_blk = d_val_block_val;
     a.B = d_B; a.ldb = ldb; a.C = d_C; a.ldc = ldc;
     a.scratch = static_cast<float*>(d_scratch);
-    a.M = M; a.N = N; a.relu = ((epilogue & 0xff) == MASK_EPILOGUE_RELU);
+    a.M = M; a.K = K; a.N = N; a.relu = ((epilogue & 0xff) == MASK_EPILOGUE_RELU);
     a.tf32x3 = (epilogue & MASK_NUMERICS_TF32X3) ? 1 : 0;
     return launch_spmm<kFmtSrbcrs>(plan, a, static_cast<cudaStream_t>(stream));
 }
@@ -460,7 +468,7 @@ extern "C" int mask_spmm_metcf(const mask_plan* plan, const int32_t* d_val_soff,
     a.coo_off = d_val_coo_off; a.coo_idx = d_val_coo_idx; a.coo_val = d_val_coo_val;
     a.B = d_B; a.ldb = ldb; a.C = d_C; a.ldc = ldc;
     a.scratch = static_cast<float*>(d_scratch);
-    a.M = M; a.N = N; a.relu = ((epilogue & 0xff) == MASK_EPILOGUE_RELU);
+    a.M = M; a.K = K; a.N = N; a.relu = ((epilogue & 0xff) == MASK_EPILOGUE_RELU);
     MASK_REQUIRE(!(epilogue & MASK_NUMERICS_TF32X3), "compensated products are implemented for SR-BCRS only");
     return launch_spmm<kFmtMetcf>(plan, a, static_cast<cudaStream_t>(stream));
 }
@@ -484,7 +492,7 @@ extern "C" int mask_spmm_mco(const mask_plan* plan, const int32_t* d_val_soff, c
     a.mco_mask = reinterpret_cast<const unsigned long long*>(d_val_mco_mask);
     a.B = d_B; a.ldb = ldb; a.C = d_C; a.ldc = ldc;
     a.scratch = static_cast<float*>(d_scratch);
-    a.M = M; a.N = N; a.relu = ((epilogue & 0xff) == MASK_EPILOGUE_RELU);
+    a.M = M; a.K = K; a.N = N; a.relu = ((epilogue & 0xff) == MASK_EPILOGUE_RELU);
     MASK_REQUIRE(!(epilogue & MASK_NUMERICS_TF32X3), "compensated products are implemented for SR-BCRS only");
     return launch_spmm<kFmtMco>(plan, a, static_cast<cudaStream_t>(stream));
 }

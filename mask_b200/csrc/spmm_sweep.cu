@@ -297,6 +297,12 @@ __global__ void __launch_bounds__(kSweepThreads, 2) spmm_sweep_kernel(const Spmm
     } else if (warp == 4) {
         // ------------------------------ MMA issuer (one lane) ------------------------------------------
         if (lane == 0) {
+            // This one thread paces the block, so its path per tile is kept to a handful of instructions:
+            // descriptors are stepped by adding to their low halves, fragment boundaries cost a compare.
+            const uint64_t a0 = umma_smem_desc(base + L::kB, 64, 32, kSwizzle128B32B);
+            const uint64_t b0 = umma_smem_desc(base + L::kA, 1, 16, kSwizzle32B);
+            const uint32_t a_hi = (uint32_t)(a0 >> 32), b_hi = (uint32_t)(b0 >> 32);
+            uint32_t a_lo = (uint32_t)a0, b_lo = (uint32_t)b0;     // of stage s
             int s = 0;
             uint32_t round = 0, acc_it = 0;
             bool ok = true;
@@ -307,7 +313,8 @@ __global__ void __launch_bounds__(kSweepThreads, 2) spmm_sweep_kernel(const Spmm
                 int t = p.group_tile[g];
                 int f_end_tile = p.frag_off[f + 1];                               // end of fragment f
                 int f_next_end = p.frag_off[min((int64_t)f + 2, p.n_frag)];      // end of fragment f + 1, loaded ahead
-                bool open = false;                                                // the fragment has MMAs in flight
+                uint32_t open = 0;                                                // 1 while the fragment has MMAs in flight
+                uint32_t acc = tmem_base;                                         // accumulator of the open fragment
                 uint32_t buf = 0;
                 while (t < t1) {
                     const int cnt = min(KT, t1 - t);
@@ -315,33 +322,34 @@ __global__ void __launch_bounds__(kSweepThreads, 2) spmm_sweep_kernel(const Spmm
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                     for (int u = 0; u < KT; u++) {
-                        if (u < cnt && ok) {
-                            while (t >= f_end_tile) {   // on to the fragment that holds tile t (fragments without tiles are skipped)
-                                if (open) { umma_commit(accf_bar(buf)); acc_it++; open = false; }
-                                f++;
-                                f_end_tile = f_next_end;
-                                f_next_end = p.frag_off[min((int64_t)f + 2, p.n_frag)];
-                            }
-                            if (!open) {
+                        if (u < cnt) {
+                            if (t >= f_end_tile || !open) {
+                                while (t >= f_end_tile) {   // on to the fragment that holds tile t (fragments without tiles are skipped)
+                                    if (open) { umma_commit(accf_bar(buf)); acc_it++; open = 0; }
+                                    f++;
+                                    f_end_tile = f_next_end;
+                                    f_next_end = p.frag_off[min((int64_t)f + 2, p.n_frag)];
+                                }
                                 buf = acc_it % NACC;
-                                if (acc_it >= (uint32_t)NACC && !mbar_wait(acce_bar(buf), (acc_it / NACC - 1) & 1, abort_flag)) ok = false;
+                                acc = tmem_base + buf * kAccCols;
+                                if (acc_it >= (uint32_t)NACC && !mbar_wait(acce_bar(buf), (acc_it / NACC - 1) & 1, abort_flag)) { ok = false; break; }
                                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                             }
-                            if (ok) {
-                                const uint64_t bdesc = umma_smem_desc(base + L::kA + s * L::kStageA + u * 512, 1, 16, kSwizzle32B);
 #pragma unroll
-                                for (int sl = 0; sl < NSLAB; sl++) {
-                                    const uint64_t adesc = umma_smem_desc(base + L::kB + s * L::kStageB + (u * NSLAB + sl) * 4096, 64, 32, kSwizzle128B32B);
-                                    umma_tf32(tmem_base + buf * kAccCols + sl * 16, adesc, bdesc, open ? 1u : 0u);
-                                }
-                                open = true;
-                                t++;
-                            }
+                            for (int sl = 0; sl < NSLAB; sl++)
+                                umma_tf32_split(acc + sl * 16, a_lo + (u * NSLAB + sl) * (4096 >> 4), a_hi, b_lo + u * (512 >> 4), b_hi, open);
+                            open = 1;
+                            t++;
                         }
                     }
                     if (!ok) break;
                     umma_commit(empty_bar(s));   // the slot is free once these MMAs have read it
-                    if (++s == S) { s = 0; round++; }
+                    a_lo += L::kStageB >> 4;
+                    b_lo += L::kStageA >> 4;
+                    if (++s == S) {
+                        s = 0; round++;
+                        a_lo = (uint32_t)a0; b_lo = (uint32_t)b0;
+                    }
                 }
                 if (open) { umma_commit(accf_bar(buf)); acc_it++; }
             }

@@ -27,12 +27,37 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-suspending probe of a phase (one instruction, returns at once).
+__device__ __forceinline__ bool mbar_probe(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: false if the block is aborting (this wait or somebody else's ran out of time).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_test(bar, parity)) return true;
     const long long start = clock64();
     while (true) {
         if (mbar_test(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - start > kUmmaWaitCycles) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+// Bounded wait that spins on the probe instead of letting the hardware park the thread: the lowest
+// wake-up latency, at the price of issue slots; for the one thread that paces a block.
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    const long long start = clock64();
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 64; i++)
+            if (mbar_probe(bar, parity)) return true;
         if (*abort_flag) return false;
         if (clock64() - start > kUmmaWaitCycles) {
             *abort_flag = 1;
@@ -56,6 +81,16 @@ __device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint6
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(kUmmaIdesc), "r"(accumulate)
+        : "memory");
+}
+// The same MMA with each descriptor given as its two 32-bit halves: the low half carries the start
+// address (>> 4), so stepping through operands that lie at fixed distances is one 32-bit add.
+__device__ __forceinline__ void umma_tf32_split(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                                uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tmov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\tsetp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %5, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(kUmmaIdesc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {

@@ -116,9 +116,13 @@ class PackedSRBCRS:
             self.plans[key] = self.new_plan(policy, group_tiles)
         return self.plans[key]
 
-    def new_plan(self, policy: str = "auto", group_tiles: int = 0) -> Plan:
-        """A plan for this matrix; carries the row map when the rows were reordered."""
+    def new_plan(self, policy: str = "auto", group_tiles: int = 0, prepare: bool = True) -> Plan:
+        """A plan for this matrix; carries the row map when the rows were reordered and, for SR-BCRS,
+        the rounded copy of the tile values that the TMA-fed kernel reads (``prepare``; costs as much
+        device memory as val_block_val again)."""
         p = Plan(self.val_soff, self.M, self.T, policy, group_tiles)
+        if prepare and isinstance(self, PackedSRBCRS) and self.T > 0:
+            check(lib().mask_plan_prepare_values(p._h, _ptr(self.val_block_val), _stream()), "mask_plan_prepare_values")
         if self.row_order is not None:
             check(lib().mask_plan_set_row_map(p._h, _ptr(self.row_order)), "mask_plan_set_row_map")
             p._row_order = self.row_order  # keep the array alive as long as the plan

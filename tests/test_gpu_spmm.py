@@ -312,10 +312,21 @@ def test_srbcrs_spmm_tcgen05_kernel(oracle_mod, name, N, gt, nslab):
         engine.spmm(pm, Bd, out=out3, plan=plan)
         out4 = torch.full((m.M, N), float("nan"), device="cuda")
         engine.spmm(pc, Bd, out=out4, plan=plan)
+        # the TMA-fed kernel: a plan that holds the rounded tile values
+        engine.tune("tma", 1)
+        plan_t = p.new_plan("auto", gt)
+        assert engine.kernel_signature(p, N, plan_t)[0].startswith("spmm_tma_kernel") or p.T == 0
+        out5 = torch.full((m.M, N), float("nan"), device="cuda")
+        engine.spmm(p, Bd, out=out5, plan=plan_t)
+        out6 = torch.full((m.M, N), float("nan"), device="cuda")
+        engine.spmm(p, Bd, out=out6, plan=plan_t, relu=True)
     finally:
         engine.tune("nslab", 0)
         engine.tune("stream_c", 0)
-    assert plan.status() == 0
+        engine.tune("tma", 0)
+    assert plan.status() == 0 and plan_t.status() == 0
+    _assert_close(oracle_mod, m, B, out5.cpu().numpy())
+    assert torch.equal(torch.relu(out5), out6)
     _assert_close(oracle_mod, m, B, out.cpu().numpy())
     _assert_close(oracle_mod, m, B, out3.cpu().numpy())
     _assert_close(oracle_mod, m, B, out4.cpu().numpy())
