@@ -153,8 +153,8 @@ constexpr int kUmmaMaxGroupTiles = 256;
 int launch_spmm_umma(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int variant);
 
 // spmm_sweep.cu: persistent tcgen05 kernel, any N % 4 == 0, groups of any length.  nslab = 128-column
-// slabs per column block (1, 2, 4; 0 = by N); stream_c = streaming stores of C.
-int launch_spmm_sweep(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int nslab, bool stream_c);
+// slabs per column block (1, 2, 4; 0 = by N).
+int launch_spmm_sweep(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int nslab);
 
 // spmm_tma.cu: persistent tcgen05 kernel fed by the tensor memory accelerator (SR-BCRS with a prepared
 // plan, see mask_plan_prepare_values).

@@ -338,7 +338,7 @@ static int launch_spmm(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
         return launch_fixup(plan, a, st);
     }
     if (g_tune_sweep != 0) {
-        int rc = launch_spmm_sweep(plan, a, st, g_tune_nslab != 0 ? g_tune_nslab : plan->nslab, g_tune_stream_c != 0);
+        int rc = launch_spmm_sweep(plan, a, st, g_tune_nslab != 0 ? g_tune_nslab : plan->nslab);
         if (rc != MASK_OK) return rc;
         return launch_fixup(plan, a, st);
     }

@@ -20,16 +20,25 @@
 //   * The block lives for the whole launch: barriers, tensor memory and the pipeline are set up
 //     once, not once per group, and groups can be as long as the planner likes.
 //   * Column ids are not staged in shared memory: a producer warp loads the ids of a step with one
-//     coalesced load four steps ahead and hands them out with shuffles.
+//     coalesced load and hands them out with shuffles.
 //   * Any N % 4 == 0: units are filled only where the column exists and the epilogue stores only
 //     such columns (tensor-memory lanes of missing columns hold garbage that is never read).
 //
-// Roles (352 threads): warps 0-3 epilogue (tensor-memory lanes 32w..32w+31 = columns of a slab),
-// warp 4 issues the MMAs (one lane), warps 5-6 prepare alternate steps (round the tile values to
-// TF32 / expand ME-TCF and MCO tiles, then fence.proxy.async: cp.async writes through the generic
-// proxy), warps 7-10 produce.  Rings: full[s] (producers -> prepare), ready[s] (prepare -> MMA),
-// empty[s] (tcgen05.commit -> producers), acc_full / acc_empty[NACC] (accumulator buffers of
-// 16*NSLAB tensor-memory columns, so the epilogue of a window overlaps the MMAs of the next ones).
+// Roles (288 threads): warps 0-3 epilogue (tensor-memory lanes 32w..32w+31 = columns of a slab),
+// warp 4 issues the MMAs (one lane), warps 5-8 produce.  A producer warp owns every fourth step WHOLE:
+// it waits for the slot, gathers the step's 16 KB with cp.async (lane -> (row, 16-byte chunk), so
+// every quarter-warp reads one contiguous 128-byte line of B and writes one bank-conflict-free row of
+// the swizzled operand), copies the tile operand(s), and -- when it comes back four steps later --
+// waits for its own copies of the previous step (cp.async.wait_group), rounds the tile values to
+// TF32 in place (each lane the 16 bytes it copied itself; ME-TCF / MCO tiles are expanded here),
+// issues the fence.proxy.async that cp.async data needs before the tensor core may read it, and
+// signals ready[s].  Compared with splitting every step over all producer warps this costs a third
+// of the instructions (the per-step bookkeeping is paid by one warp, not four), needs no separate
+// preparation warps and no "landed" barrier, and the look-ahead of the column ids comes for free:
+// a warp loads the ids of its next step while it works on the current one.  Rings: ready[s]
+// (producer -> MMA), empty[s] (tcgen05.commit -> producers), acc_full / acc_empty[NACC]
+// (accumulator buffers of 16*NSLAB tensor-memory columns, so the epilogue of a window overlaps
+// the MMAs of the next ones).
 //
 // Every wait is bounded (about a second of SM clock).  On expiry the block raises its abort flag and
 // the plan's device status word; every role leaves its loops, the producers wait for their copies,
@@ -40,7 +49,7 @@
 
 namespace mask {
 
-constexpr int kSweepThreads = 352;
+constexpr int kSweepThreads = 288;
 
 template <int NSLAB, int FMT>
 struct SweepLayout {
@@ -58,8 +67,8 @@ struct SweepLayout {
     static constexpr int kB = 0;
     static constexpr int kA = S * kStageB;
     static constexpr int kCoo = kA + S * kStageA;
-    static constexpr int kBars = kCoo + ((S * KT * kCooStride + 15) & ~15);   // full[S], empty[S], ready[S], acc_full[NACC], acc_empty[NACC], drain
-    static constexpr int kNumBars = 3 * S + 2 * kNacc + 1;
+    static constexpr int kBars = kCoo + ((S * KT * kCooStride + 15) & ~15);   // empty[S], ready[S], acc_full[NACC], acc_empty[NACC], drain
+    static constexpr int kNumBars = 2 * S + 2 * kNacc + 1;
     static constexpr int kTmemSlot = kBars + kNumBars * 8;
     static constexpr int kAbort = kTmemSlot + 8;
     static constexpr int kBytes = kAbort + 8;
@@ -76,23 +85,21 @@ __device__ __forceinline__ bool mbar_wait_drain(uint32_t bar, uint32_t parity) {
     return true;
 }
 
-template <int NSLAB, int FMT, bool STREAM_C>
+template <int NSLAB, int FMT>
 __global__ void __launch_bounds__(kSweepThreads, 2) spmm_sweep_kernel(const SpmmArgs p, int32_t* status) {
     constexpr bool METCF = FMT == kFmtMetcf, MCO = FMT == kFmtMco;
     using L = SweepLayout<NSLAB, FMT>;
     constexpr int KT = L::KT, S = L::S, NACC = L::kNacc, kAccCols = L::kAccCols;
-    constexpr int kLook = 4;                                        // steps the column ids are loaded ahead
     extern __shared__ unsigned char sweep_smem_raw[];
     const uint32_t raw = (uint32_t)__cvta_generic_to_shared(sweep_smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;                   // swizzle patterns are functions of the address bits
     unsigned char* gbase = sweep_smem_raw + (base - raw);
     const uint32_t bars = base + L::kBars;
-    auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (S + s); };
-    auto ready_bar = [&](int s) { return bars + 8u * (2 * S + s); };
-    auto accf_bar = [&](int b) { return bars + 8u * (3 * S + b); };
-    auto acce_bar = [&](int b) { return bars + 8u * (3 * S + NACC + b); };
-    const uint32_t drain_bar = bars + 8u * (3 * S + 2 * NACC);
+    auto empty_bar = [&](int s) { return bars + 8u * s; };
+    auto ready_bar = [&](int s) { return bars + 8u * (S + s); };
+    auto accf_bar = [&](int b) { return bars + 8u * (2 * S + b); };
+    auto acce_bar = [&](int b) { return bars + 8u * (2 * S + NACC + b); };
+    const uint32_t drain_bar = bars + 8u * (2 * S + 2 * NACC);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + L::kAbort);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + L::kTmemSlot);
 
@@ -103,9 +110,8 @@ __global__ void __launch_bounds__(kSweepThreads, 2) spmm_sweep_kernel(const Spmm
     if (tid == 0) {
         *abort_flag = 0;
         for (int s = 0; s < S; s++) {
-            mbar_init(full_bar(s), 128);   // one deferred arrive per producer thread
             mbar_init(empty_bar(s), 1);    // tcgen05.commit
-            mbar_init(ready_bar(s), 1);    // lane 0 of the preparing warp
+            mbar_init(ready_bar(s), 1);    // lane 0 of the producing warp
         }
         for (int b = 0; b < NACC; b++) {
             mbar_init(accf_bar(b), 1);     // tcgen05.commit
@@ -132,168 +138,160 @@ __global__ void __launch_bounds__(kSweepThreads, 2) spmm_sweep_kernel(const Spmm
         return (cb & 1) ? G - 1 - gi : gi;
     };
 
-    if (warp >= 7) {
-        // ------------------------------ producers ------------------------------------------------
-        const int pw = warp - 7;                 // this warp copies 32-column atom pw of every unit
+    if (warp >= 5) {
+        // ------------------------------ producers (each warp owns every fourth step) -------------------
+        const int pw = warp - 5;
         const int lr = lane >> 3, lc = lane & 7; // row (and row + 4), 16-byte chunk
-        const uint32_t off0 = (uint32_t)(pw * 1024 + lr * 128 + ((lc ^ (2 * lr)) * 16));   // 32-byte chunks swizzled by row % 4
+        const uint32_t off0 = (uint32_t)(lr * 128 + ((lc ^ (2 * lr)) * 16));   // 32-byte chunks swizzled by row % 4
         const uint32_t ldb_bytes = (uint32_t)(p.ldb * 4);
-        const int idl = lane & (8 * KT - 1);     // which of the step's 8*KT ids this lane loads
-        int s = 0;
-        uint32_t round = 0;
+        const int idl = lane & (8 * KT - 1);     // which of a step's 8*KT ids this lane loads
+        uint32_t gstep = 0;                      // steps of the items before the current one
+        int pend_s = -1, pend_cnt = 0;           // this warp's last step: copies issued, not yet handed to the MMA thread
         bool ok = true;
+
+        // Hands a landed step over: round / expand the tile operand(s), make the copies visible to the
+        // tensor core's proxy, signal ready.
+        auto finish = [&](int s, int cnt) {
+#pragma unroll
+            for (int u = 0; u < KT; u++) {
+                if (u < cnt) {
+                    unsigned char* aslot = gbase + L::kA + s * L::kStageA + u * 512;
+                    if (METCF) {  // rebuild the 16x8 operand: zero, then tile[idx] = rna(value) over the run
+                        __syncwarp();   // the staged run was copied by other lanes
+                        const unsigned char* st = gbase + L::kCoo + (s * KT + u) * L::kCooStride;
+                        uint32_t* tile = reinterpret_cast<uint32_t*>(aslot);
+                        reinterpret_cast<uint4*>(tile)[lane] = make_uint4(0u, 0u, 0u, 0u);
+                        __syncwarp();
+                        const int2 run = *reinterpret_cast<const int2*>(st + L::kRunAt);
+                        const int rcnt = run.y - run.x;
+                        const int* sidx = reinterpret_cast<const int*>(st);
+                        const uint32_t* sval = reinterpret_cast<const uint32_t*>(st + 128);
+                        if (lane < rcnt) tile[sidx[lane]] = sval[lane] + 0x1000u;
+                        for (int e = run.x + 32 + lane; e < run.y; e += 32)   // dense tiles: entries beyond the staged 32
+                            tile[__ldg(p.coo_idx + e)] = __float_as_uint(__ldg(p.coo_val + e)) + 0x1000u;
+                    } else if (MCO) {
+                        __syncwarp();   // mask and values were copied by other lanes
+                        const unsigned char* st = gbase + L::kCoo + (s * KT + u) * L::kCooStride;
+                        const ulonglong2 m = *reinterpret_cast<const ulonglong2*>(st);
+                        reinterpret_cast<uint4*>(aslot)[lane] = mco_expand(m.x, m.y, reinterpret_cast<const uint32_t*>(st + 16), lane);
+                    } else {  // round the tile values to TF32 (nearest, ties away) in place: each lane its own 16 bytes
+                        uint4* at = reinterpret_cast<uint4*>(aslot) + lane;
+                        uint4 v = *at;
+                        v.x += 0x1000u; v.y += 0x1000u; v.z += 0x1000u; v.w += 0x1000u;
+                        *at = v;
+                    }
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(ready_bar(s));
+        };
+
         for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const int cb = item_cb(item);
             const int g = item_group(item, cb);
             const int t0 = p.group_tile[g], t1 = p.group_tile[g + 1];
-            const int colt = cb * (128 * NSLAB) + 32 * pw + 4 * lc;   // this thread's column in slab 0
-            const char* Bcol = reinterpret_cast<const char*>(p.B + colt);
-            bool valid[NSLAB];
-#pragma unroll
-            for (int sl = 0; sl < NSLAB; sl++) valid[sl] = colt + 128 * sl < p.N;
-            auto load_ids = [&](int tb) -> int {
-                const int64_t at = (int64_t)tb * kTileCols + idl;
-                return at < (int64_t)t1 * kTileCols ? __ldg(p.val_sidx + at) : 0;
+            const int n_steps = (t1 - t0 + KT - 1) / KT;
+            const int cols_left = p.N - cb * (128 * NSLAB) - 4 * lc;    // > 32 j: this thread's chunk of 32-column atom j exists
+            const bool whole = p.N - cb * (128 * NSLAB) >= 128 * NSLAB; // every column of the block exists
+            const char* Bcol = reinterpret_cast<const char*>(p.B + cb * (128 * NSLAB) + 4 * lc);
+            auto load_ids = [&](int j) -> int {
+                const int64_t at = ((int64_t)t0 + (int64_t)j * KT) * kTileCols + idl;
+                return (j < n_steps && at < (int64_t)t1 * kTileCols) ? __ldg(p.val_sidx + at) : 0;
             };
-            // ME-TCF / MCO: [begin, end) of the value run of tile tb + lane, loaded ahead like the ids
-            auto load_run = [&](int tb) -> int2 {
+            // ME-TCF / MCO: [begin, end) of the value run of tile (step j, lane), loaded ahead like the ids
+            auto load_run = [&](int j) -> int2 {
                 int2 r = make_int2(0, 0);
                 if (FMT != kFmtSrbcrs) {
-                    const int64_t tile = (int64_t)tb + lane;
-                    if (lane < KT && tile < t1) {
+                    const int64_t tile = (int64_t)t0 + (int64_t)j * KT + lane;
+                    if (j < n_steps && lane < KT && tile < t1) {
                         if (METCF) r = __ldg(reinterpret_cast<const int2*>(p.coo_off) + tile);
                         else r = make_int2(__ldg(p.coo_off + tile), __ldg(p.coo_off + tile + 1));
                     }
                 }
                 return r;
             };
-            // One pipeline step.  q / rq hold the ids / value runs of this step (loaded four steps ago);
-            // they are handed out with shuffles first and then REFILLED IN PLACE for the step four ahead, so
-            // a queue register is written by a load and read four steps later and never moved: a move
-            // would wait for the load it carries and put one memory latency into every step.
-            auto produce = [&](int tb, int& q, int2& rq) -> bool {
+            const int j0 = (int)((pw - gstep) & 3u);   // this warp's first step of the item
+            int q = load_ids(j0);
+            int2 rq = load_run(j0);
+            for (int j = j0; j < n_steps; j += 4) {
+                const int tb = t0 + j * KT;
                 const int cnt = min(KT, t1 - tb);
+                const uint32_t gi = gstep + (uint32_t)j;
+                const int s = (int)(gi % S);
+                const uint32_t round = gi / S;
                 int id0[KT], id1[KT];
 #pragma unroll
                 for (int u = 0; u < KT; u++) {
                     id0[u] = __shfl_sync(0xffffffffu, q, u * kTileCols + lr);
                     id1[u] = __shfl_sync(0xffffffffu, q, u * kTileCols + lr + 4);
                 }
-                int2 run = make_int2(0, 0);
-                if (FMT != kFmtSrbcrs) run = make_int2(__shfl_sync(0xffffffffu, rq.x, pw), __shfl_sync(0xffffffffu, rq.y, pw));
-                q = load_ids(tb + kLook * KT);
-                rq = load_run(tb + kLook * KT);
-                // the verdict of a wait is made warp-uniform: every lane takes part in the next step's shuffles
-                if (round > 0 && !__all_sync(0xffffffffu, mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag))) return false;
+                int2 run[KT];
+                if (FMT != kFmtSrbcrs) {
+#pragma unroll
+                    for (int u = 0; u < KT; u++) run[u] = make_int2(__shfl_sync(0xffffffffu, rq.x, u), __shfl_sync(0xffffffffu, rq.y, u));
+                }
+                q = load_ids(j + 4);        // the ids of this warp's next step travel while it works on this one
+                rq = load_run(j + 4);
+                // the verdict of a wait is made warp-uniform: every lane takes part in the shuffles above
+                if (round > 0 && !__all_sync(0xffffffffu, mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag))) { ok = false; break; }
                 const uint32_t dst = base + L::kB + s * L::kStageB + off0;
 #pragma unroll
                 for (int u = 0; u < KT; u++) {
                     if (u < cnt) {
                         const char* r0 = Bcol + (uint64_t)(uint32_t)id0[u] * ldb_bytes;
                         const char* r1 = Bcol + (uint64_t)(uint32_t)id1[u] * ldb_bytes;
+                        if (whole) {
 #pragma unroll
-                        for (int sl = 0; sl < NSLAB; sl++) {
-                            if (valid[sl]) {
-                                cp16(dst + (u * NSLAB + sl) * 4096, r0 + sl * 512);
-                                cp16(dst + (u * NSLAB + sl) * 4096 + 512, r1 + sl * 512);
+                            for (int a4 = 0; a4 < 4 * NSLAB; a4++) {   // 32-column atom a4 of the block: unit a4 / 4, atom a4 % 4
+                                cp16(dst + u * NSLAB * 4096 + a4 * 1024, r0 + a4 * 128);
+                                cp16(dst + u * NSLAB * 4096 + a4 * 1024 + 512, r1 + a4 * 128);
+                            }
+                        } else {
+#pragma unroll
+                            for (int a4 = 0; a4 < 4 * NSLAB; a4++) {
+                                if (cols_left > 32 * a4) {
+                                    cp16(dst + u * NSLAB * 4096 + a4 * 1024, r0 + a4 * 128);
+                                    cp16(dst + u * NSLAB * 4096 + a4 * 1024 + 512, r1 + a4 * 128);
+                                }
                             }
                         }
-                    }
-                }
-                // tile operand(s): warp u copies the one of tile u of the step
-                if (pw < cnt) {
-                    const int64_t tile = tb + pw;
-                    if (METCF) {
-                        // [begin, end) of the run, then its first 32 entries (runs start on multiples of 8
-                        // entries and are padded to 8)
-                        const uint32_t st = base + L::kCoo + (s * KT + pw) * L::kCooStride;
-                        if (lane == 16)
-                            asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(st + L::kRunAt), "l"(p.coo_off + 2 * tile) : "memory");
-                        const int chunk = lane & 7;   // 4 entries
-                        if (lane < 16 && run.x + 4 * chunk < ((run.y + 7) & ~7)) {
-                            const void* src = lane < 8 ? static_cast<const void*>(p.coo_idx + run.x + 4 * chunk)
-                                                       : static_cast<const void*>(p.coo_val + run.x + 4 * chunk);
-                            cp16(st + lane * 16, src);
+                        // the tile operand, or what it is rebuilt from
+                        const int64_t tile = (int64_t)tb + u;
+                        if (METCF) {
+                            // [begin, end) of the run, then its first 32 entries (runs start on multiples of 8
+                            // entries and are padded to 8)
+                            const uint32_t st = base + L::kCoo + (s * KT + u) * L::kCooStride;
+                            if (lane == 16)
+                                asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(st + L::kRunAt), "l"(p.coo_off + 2 * tile) : "memory");
+                            const int chunk = lane & 7;   // 4 entries
+                            if (lane < 16 && run[u].x + 4 * chunk < ((run[u].y + 7) & ~7)) {
+                                const void* src = lane < 8 ? static_cast<const void*>(p.coo_idx + run[u].x + 4 * chunk)
+                                                           : static_cast<const void*>(p.coo_val + run[u].x + 4 * chunk);
+                                cp16(st + lane * 16, src);
+                            }
+                        } else if (MCO) {
+                            const uint32_t st = base + L::kCoo + (s * KT + u) * L::kCooStride;
+                            if (lane == 0) cp16(st, p.mco_mask + 2 * tile);
+                            if (lane < 2)
+                                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(st + L::kRunAt + 4 * lane), "l"(p.coo_off + tile + lane) : "memory");
+                            if (run[u].x + 4 * lane < run[u].y) cp16(st + 16 + lane * 16, p.coo_val + run[u].x + 4 * lane);   // runs are multiples of 4 values
+                        } else {
+                            cp16(base + L::kA + s * L::kStageA + u * 512 + lane * 16, p.val_blk + tile * kTileElems + lane * 4);
                         }
-                    } else if (MCO) {
-                        const uint32_t st = base + L::kCoo + (s * KT + pw) * L::kCooStride;
-                        const int o0 = run.x, o1 = run.y;
-                        if (lane == 0) cp16(st, p.mco_mask + 2 * tile);
-                        if (lane < 2)
-                            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(st + L::kRunAt + 4 * lane), "l"(p.coo_off + tile + lane) : "memory");
-                        if (o0 + 4 * lane < o1) cp16(st + 16 + lane * 16, p.coo_val + o0 + 4 * lane);   // runs are multiples of 4 values
-                    } else {
-                        cp16(base + L::kA + s * L::kStageA + pw * 512 + lane * 16, p.val_blk + tile * kTileElems + lane * 4);
                     }
                 }
-                // arrives on full[s] once every copy this thread has issued so far has landed
-                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(full_bar(s)) : "memory");
-                if (++s == S) { s = 0; round++; }
-                return true;
-            };
-            static_assert(kLook == 4, "the queues below are four deep");
-            int q0 = load_ids(t0), q1 = load_ids(t0 + KT), q2 = load_ids(t0 + 2 * KT), q3 = load_ids(t0 + 3 * KT);
-            int2 r0q = load_run(t0), r1q = load_run(t0 + KT), r2q = load_run(t0 + 2 * KT), r3q = load_run(t0 + 3 * KT);
-            for (int tb = t0; tb < t1; tb += 4 * KT) {
-                if (!produce(tb, q0, r0q)) { ok = false; break; }
-                if (tb + KT >= t1) break;
-                if (!produce(tb + KT, q1, r1q)) { ok = false; break; }
-                if (tb + 2 * KT >= t1) break;
-                if (!produce(tb + 2 * KT, q2, r2q)) { ok = false; break; }
-                if (tb + 3 * KT >= t1) break;
-                if (!produce(tb + 3 * KT, q3, r3q)) { ok = false; break; }
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                if (pend_s >= 0) {   // the step this warp issued four steps ago has had that long to land
+                    asm volatile("cp.async.wait_group 1;" ::: "memory");
+                    finish(pend_s, pend_cnt);
+                }
+                pend_s = s; pend_cnt = cnt;
             }
+            gstep += (uint32_t)n_steps;
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
-    } else if (warp >= 5) {
-        // ------------------------------ prepare (two warps, alternate steps) -------------------------
-        const int q = warp - 5;
-        int s = 0;
-        uint32_t round = 0, step = 0;
-        bool ok = true;
-        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-            const int g = item_group(item, item_cb(item));
-            const int t0 = p.group_tile[g], t1 = p.group_tile[g + 1];
-            for (int tb = t0; tb < t1; tb += KT, step++) {
-                const int cnt = min(KT, t1 - tb);
-                if ((step & 1) == (uint32_t)q) {
-                    if (!__all_sync(0xffffffffu, mbar_wait(full_bar(s), round & 1, abort_flag))) { ok = false; break; }
-#pragma unroll
-                    for (int u = 0; u < KT; u++) {
-                        if (u < cnt) {
-                            unsigned char* aslot = gbase + L::kA + s * L::kStageA + u * 512;
-                            if (METCF) {  // rebuild the 16x8 operand: zero, then tile[idx] = rna(value) over the run
-                                const unsigned char* st = gbase + L::kCoo + (s * KT + u) * L::kCooStride;
-                                uint32_t* tile = reinterpret_cast<uint32_t*>(aslot);
-                                reinterpret_cast<uint4*>(tile)[lane] = make_uint4(0u, 0u, 0u, 0u);
-                                __syncwarp();
-                                const int2 run = *reinterpret_cast<const int2*>(st + L::kRunAt);
-                                const int rcnt = run.y - run.x;
-                                const int* sidx = reinterpret_cast<const int*>(st);
-                                const uint32_t* sval = reinterpret_cast<const uint32_t*>(st + 128);
-                                if (lane < rcnt) tile[sidx[lane]] = sval[lane] + 0x1000u;
-                                for (int e = run.x + 32 + lane; e < run.y; e += 32)   // dense tiles: entries beyond the staged 32
-                                    tile[__ldg(p.coo_idx + e)] = __float_as_uint(__ldg(p.coo_val + e)) + 0x1000u;
-                                __syncwarp();
-                            } else if (MCO) {
-                                const unsigned char* st = gbase + L::kCoo + (s * KT + u) * L::kCooStride;
-                                const ulonglong2 m = *reinterpret_cast<const ulonglong2*>(st);
-                                reinterpret_cast<uint4*>(aslot)[lane] = mco_expand(m.x, m.y, reinterpret_cast<const uint32_t*>(st + 16), lane);
-                            } else {  // round the tile values to TF32 (nearest, ties away) in place
-                                uint4* at = reinterpret_cast<uint4*>(aslot) + lane;
-                                uint4 v = *at;
-                                v.x += 0x1000u; v.y += 0x1000u; v.z += 0x1000u; v.w += 0x1000u;
-                                *at = v;
-                            }
-                        }
-                    }
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(ready_bar(s));
-                }
-                if (++s == S) { s = 0; round++; }
-            }
-        }
+        if (ok && pend_s >= 0) finish(pend_s, pend_cnt);
     } else if (warp == 4) {
         // ------------------------------ MMA issuer (one lane) ------------------------------------------
         if (lane == 0) {
@@ -428,8 +426,7 @@ __global__ void __launch_bounds__(kSweepThreads, 2) spmm_sweep_kernel(const Spmm
 #pragma unroll
                             for (int sl = 0; sl < NSLAB; sl++) {
                                 if (colok[sl]) {
-                                    if (STREAM_C && slot < 0 && d == 0) __stcs(cb_ptr + off + col + 128 * sl, __uint_as_float(v[sl][i]));
-                                    else cb_ptr[off + col + 128 * sl] = __uint_as_float(v[sl][i]);
+                                    cb_ptr[off + col + 128 * sl] = __uint_as_float(v[sl][i]);
                                 }
                             }
                         }
@@ -449,11 +446,11 @@ __global__ void __launch_bounds__(kSweepThreads, 2) spmm_sweep_kernel(const Spmm
     if (tid == 0 && *abort_flag) atomicExch(status, 1);
 }
 
-template <int NSLAB, int FMT, bool STREAM_C>
+template <int NSLAB, int FMT>
 static int launch_sweep_variant(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
     using L = SweepLayout<NSLAB, FMT>;
     static_assert(2 * (L::kDynamicBytes + 1024) <= 228 * 1024, "two blocks per SM");
-    auto kern = spmm_sweep_kernel<NSLAB, FMT, STREAM_C>;
+    auto kern = spmm_sweep_kernel<NSLAB, FMT>;
     MASK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));   // per device
     MASK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     // Two blocks per SM by construction: shared memory (asserted above), registers (launch bounds) and
@@ -471,19 +468,14 @@ static int launch_sweep_variant(const mask_plan* plan, SpmmArgs a, cudaStream_t 
 }
 
 template <int FMT>
-static int launch_sweep_fmt(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int nslab, bool stream_c) {
-    if (stream_c) {
-        if (nslab == 1) return launch_sweep_variant<1, FMT, true>(plan, a, st);
-        if (nslab == 2) return launch_sweep_variant<2, FMT, true>(plan, a, st);
-        return launch_sweep_variant<4, FMT, true>(plan, a, st);
-    }
-    if (nslab == 1) return launch_sweep_variant<1, FMT, false>(plan, a, st);
-    if (nslab == 2) return launch_sweep_variant<2, FMT, false>(plan, a, st);
-    return launch_sweep_variant<4, FMT, false>(plan, a, st);
+static int launch_sweep_fmt(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int nslab) {
+    if (nslab == 1) return launch_sweep_variant<1, FMT>(plan, a, st);
+    if (nslab == 2) return launch_sweep_variant<2, FMT>(plan, a, st);
+    return launch_sweep_variant<4, FMT>(plan, a, st);
 }
 
 // nslab: 128-column slabs per column block (1, 2 or 4); 0 = the widest that N fills.
-int launch_spmm_sweep(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int nslab, bool stream_c) {
+int launch_spmm_sweep(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int nslab) {
     if (a.N % 4 != 0) return fail(MASK_ERR_INVALID_ARGUMENT, "N must be a multiple of 4");
     if (plan->d_group_tile == nullptr) return fail(MASK_ERR_INVALID_ARGUMENT, "plan has no group tile table");
     if (nslab != 1 && nslab != 2 && nslab != 4) nslab = a.N > 256 ? 4 : (a.N > 128 ? 2 : 1);
@@ -491,9 +483,9 @@ int launch_spmm_sweep(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st,
     b.group_tile = plan->d_group_tile;
     b.n_groups = (int32_t)plan->G;
     b.n_frag = plan->F;
-    if (a.mco_mask) return launch_sweep_fmt<kFmtMco>(plan, b, st, nslab, stream_c);
-    if (a.coo_off) return launch_sweep_fmt<kFmtMetcf>(plan, b, st, nslab, stream_c);
-    return launch_sweep_fmt<kFmtSrbcrs>(plan, b, st, nslab, stream_c);
+    if (a.mco_mask) return launch_sweep_fmt<kFmtMco>(plan, b, st, nslab);
+    if (a.coo_off) return launch_sweep_fmt<kFmtMetcf>(plan, b, st, nslab);
+    return launch_sweep_fmt<kFmtSrbcrs>(plan, b, st, nslab);
 }
 
 }  // namespace mask
