@@ -113,8 +113,9 @@ int mask_mco_fill(const int32_t* d_rowptr, const float* d_values, int32_t M, int
 /* ------------------------------------------------------------------------------------------
  * Row reorders of the Format-DSL host bridge (examples/src_fp32/acc/testbed/custom_format_e2e.cu:
  * 163-347): reverse_cuthill_mckee, first_column_order, jaccard_greedy_order, with the same
- * tie-breaks, so the orders are bit-identical.  h_row_order[new_row] = original_row.  Host
- * functions (the bridge computes them on the host too, outside its timed region).
+ * tie-breaks, so the orders are bit-identical.  d_row_order[new_row] = original_row.  Computed on
+ * the device from a device CSR matrix (rows strictly ascending, the packers' contract); the call
+ * allocates its scratch itself and synchronises the stream before it returns.
  * ------------------------------------------------------------------------------------------ */
 typedef enum mask_reorder {
     MASK_REORDER_NONE = 0,
@@ -123,8 +124,8 @@ typedef enum mask_reorder {
     MASK_REORDER_JACCARD_GREEDY = 3
 } mask_reorder;
 
-int mask_reorder_rows(int kind, const int32_t* h_rowptr, const int32_t* h_colind, int32_t M,
-                      int32_t K, int32_t* h_row_order);
+int mask_reorder_rows(int kind, const int32_t* d_rowptr, const int32_t* d_colind, int32_t M,
+                      int32_t K, int32_t* d_row_order, void* stream);
 
 /* Applies an order on the device: row i of the output CSR is row d_row_order[i] of the input
  * (what the bridge's packer does while walking row_order, custom_format_e2e.cu:554-568).
@@ -170,6 +171,22 @@ typedef struct mask_features {
 } mask_features;
 
 int mask_features_from_soff(const int32_t* h_val_soff, int32_t M, int64_t nnz, mask_features* out);
+
+/* Column-side features, computed on the device from val_sidx (8 T gathered ids): what the rows of
+ * B the product gathers look like to the L2.  Same role as the column statistics of the
+ * reference's featurizer (unique columns per window, entries per unique column,
+ * examples/src_fp32/dtc/testbed/featurize_mtx.cu:298-401), extended by what a B200 plan needs. */
+typedef struct mask_column_features {
+    int64_t gathers;          /* 8 T: rows of B fetched per sweep of the matrix */
+    int32_t distinct_columns; /* columns that hold an entry = rows of B the product touches */
+    int32_t band_p50, band_p90; /* distance of a gathered row from the diagonal position of its window
+                                   (rows of B), percentiles over all gathers, rounded up to a power of 2 */
+    int32_t hub_columns[3];   /* how many rows of B fit half the L2 at row widths of min(N,512), min(N,256), min(N,128) columns */
+    double hub_share[3];      /* share of all gathers that go to that many most gathered columns */
+    int32_t l2_bytes;
+} mask_column_features;
+int mask_features_columns(const int32_t* d_val_soff, const int32_t* d_val_sidx, int32_t M, int32_t K, int64_t T,
+                          int32_t N, mask_column_features* out, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * ME-TCF packed-format cache file, byte-compatible with the reference's storeCheckpoint /
@@ -243,6 +260,15 @@ int mask_peer_alloc(size_t bytes, void** d_ptr, void* handle);
 int mask_peer_open(const void* handle, void** d_ptr);
 int mask_peer_close(void* d_ptr);
 int mask_peer_free(void* d_ptr);
+/* The plan table: computes the column features of the packed matrix (device) and sets the plan's
+ * kernel parameters from them -- today the number of 128-column slabs a resident block sweeps at
+ * a time (4: tile values and ids read once, for matrices whose gathers are local; 2: narrower rows
+ * of B, for large power-law matrices where that lets the L2 serve more of the gathers).  Replaces
+ * the knobs the reference hands to its strategy agent (python/sparsene/op_gen/strategy_agent.py:
+ * 414-528).  Without this call a plan uses the widest block N fills.  Synchronises the stream.
+ * mask_plan_column_features returns what was measured and chosen. */
+int mask_plan_autotune(mask_plan* plan, const int32_t* d_val_soff, const int32_t* d_val_sidx, int32_t K, void* stream);
+int mask_plan_column_features(const mask_plan* plan, mask_column_features* out, int32_t* nslab_wide);
 /* Prepares the plan for the TMA-fed SpMM kernel: keeps a copy of val_block_val (128 T floats, owned
  * by the plan) with every value rounded to TF32 -- nearest, ties away, the reference kernels'
  * cvt.rna (examples/src_fp32/sr_bcrs/testbed/kernel.inc:809-814) done once per matrix instead of

@@ -25,7 +25,7 @@ SIGNATURES = {
     "mask_metcf_fill": (C.c_int, [vp, vp, vp, i32, i64, vp, vp, i64, vp, vp, i64, vp, vp, vp, vp]),
     "mask_mco_offsets": (C.c_int, [vp, i32, i64, vp, vp, i64, C.c_int, vp, vp, C.POINTER(i64), vp]),
     "mask_mco_fill": (C.c_int, [vp, vp, i32, i64, vp, vp, i64, C.c_int, vp, vp, i64, vp, vp, vp]),
-    "mask_reorder_rows": (C.c_int, [C.c_int, vp, vp, i32, i32, vp]),
+    "mask_reorder_rows": (C.c_int, [C.c_int, vp, vp, i32, i32, vp, vp]),
     "mask_csr_permute_rows": (C.c_int, [vp, vp, vp, i32, vp, vp, vp, vp, vp]),
     "mask_plan_set_row_map": (C.c_int, [vp, vp]),
     "mask_plan_set_peer_outputs": (C.c_int, [vp, vp, i32]),
@@ -46,6 +46,9 @@ SIGNATURES = {
     "mask_plan_scratch_bytes": (sz, [vp, i32]),
     "mask_plan_info": (C.c_int, [vp, C.POINTER(i64), C.POINTER(i64), C.POINTER(i64), C.POINTER(i32)]),
     "mask_plan_export": (C.c_int, [vp, vp, vp, vp]),
+    "mask_features_columns": (C.c_int, [vp, vp, i32, i32, i64, i32, vp, vp]),
+    "mask_plan_autotune": (C.c_int, [vp, vp, vp, i32, vp]),
+    "mask_plan_column_features": (C.c_int, [vp, vp, C.POINTER(i32)]),
     "mask_plan_prepare_values": (C.c_int, [vp, vp, vp]),
     "mask_plan_status": (C.c_int, [vp, C.POINTER(i32), vp]),
     "mask_spmm_srbcrs": (C.c_int, [vp, vp, vp, vp, i32, i32, i32, vp, i64, vp, i64, vp, sz, C.c_int, vp]),
@@ -73,6 +76,19 @@ class Features(C.Structure):
     _fields_ = [("row_windows", i32), ("empty_windows", i32), ("tiles", i64), ("nnz", i64), ("tiles_mean", C.c_double),
                 ("tiles_p50", i32), ("tiles_p95", i32), ("tiles_p99", i32), ("tiles_max", i32),
                 ("top5_window_share", C.c_double), ("tile_fill", C.c_double), ("heavy_tail", i32)]
+
+
+class ColumnFeatures(C.Structure):
+    """mask_column_features"""
+    _fields_ = [("gathers", i64), ("distinct_columns", i32), ("band_p50", i32), ("band_p90", i32), ("hub_columns", i32 * 3),
+                ("hub_share", C.c_double * 3), ("l2_bytes", i32)]
+
+    def as_dict(self):
+        return dict(gathers=int(self.gathers), distinct_columns=int(self.distinct_columns), band_p50=int(self.band_p50),
+                    band_p90=int(self.band_p90), hub_columns=list(self.hub_columns), hub_share=[round(x, 4) for x in self.hub_share],
+                    l2_bytes=int(self.l2_bytes))
+
+
 EPILOGUE_NONE, EPILOGUE_RELU = 0, 1
 NUMERICS_TF32X3 = 0x100   # OR-able into the epilogue argument (SR-BCRS)
 

@@ -169,7 +169,7 @@ extern "C" int mask_session_create_srbcrs(int32_t M, int32_t K, int64_t T, const
         }
         rc = mask_plan_create(s->d_soff, M, T, policy, 0, s->stream, &s->plan);
         if (rc != MASK_OK) return rc;
-        return mask_plan_prepare_values(s->plan, s->d_blk, s->stream);
+        return T > 0 ? mask_plan_autotune(s->plan, s->d_soff, s->d_sidx, K, s->stream) : MASK_OK;
     };
     int rc = body();
     if (rc != MASK_OK) { mask_session_destroy(s); return rc; }
@@ -215,7 +215,7 @@ extern "C" int mask_session_create_csr(int32_t M, int32_t K, int64_t nnz, const 
         if (rc != MASK_OK) return rc;
         rc = mask_plan_create(s->d_soff, M, s->T, policy, 0, s->stream, &s->plan);
         if (rc != MASK_OK) return rc;
-        return mask_plan_prepare_values(s->plan, s->d_blk, s->stream);
+        return s->T > 0 ? mask_plan_autotune(s->plan, s->d_soff, s->d_sidx, K, s->stream) : MASK_OK;
     };
     int rc = body();
     if (s->stream) cudaStreamSynchronize(s->stream);

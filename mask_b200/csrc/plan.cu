@@ -68,9 +68,11 @@ static int32_t default_group_tiles(int64_t T) {
     // neighbouring windows (stencils, banded matrices) are fetched from DRAM once and found in L2
     // by the other blocks.  Groups of 800 tiles measured twice as slow as groups of 128 on a
     // 27-point stencil and on a power-law graph for exactly that reason.
-    const int64_t slots = (int64_t)sm_count() * 3;
-    const int64_t g = T / (slots * 4);
-    return (int32_t)std::max<int64_t>(8, std::min<int64_t>(128, g));
+    // Small matrices: one group per resident block (every group a block takes costs it a pipeline
+    // restart, and with fewer groups than blocks nothing is left to balance).
+    const int64_t resident = (int64_t)sm_count() * 2;
+    const int64_t g = (T + resident - 1) / resident;
+    return (int32_t)std::max<int64_t>(16, std::min<int64_t>(128, g));
 }
 
 // Fills the fragment / group tables of `p` from val_soff on the host.

@@ -34,6 +34,8 @@ struct mask_plan {
     const int32_t* d_row_map = nullptr;  // optional, not owned: output row of packed row i (a row reorder's order[])
     float* const* d_peer_out = nullptr;  // optional, not owned: device array of n_peer_out extra output bases
     int32_t n_peer_out = 0;
+    mask_column_features col_features = {};   // set by mask_plan_autotune
+    int32_t has_col_features = 0;
     float* d_vals_tf32 = nullptr;        // owned: val_block_val rounded to TF32 (mask_plan_prepare_values), for the TMA kernel
     const float* vals_src = nullptr;     // the array d_vals_tf32 was made from
     int32_t* d_status = nullptr;  // device status word: non-zero after a kernel gave up on a bounded wait

@@ -332,6 +332,14 @@ static int launch_spmm(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
         if (rc != MASK_OK) return rc;
         return launch_fixup(plan, a, st);
     }
+    // Narrow products: below about 96 columns a tile's one half-empty 128-column MMA costs more than
+    // the warp-level MMAs of the shared-memory ring kernel (measured crossover on a 2^22-node power-law
+    // graph: N = 64 5.8 against 7.5 ms, N = 128 9.0 against 7.9 ms).
+    if (FMT == kFmtSrbcrs && g_tune_sweep == 1 && N < 96 && g_tune_async != 0) {
+        int rc = launch_spmm_async(plan, a, st, g_tune_nq, g_tune_stages);
+        if (rc != MASK_OK) return rc;
+        return launch_fixup(plan, a, st);
+    }
     if (g_tune_sweep != 0 && g_tune_tma != 0 && FMT == kFmtSrbcrs && spmm_tma_applies(plan, a)) {
         int rc = launch_spmm_tma(plan, a, a.K, st, g_tune_nslab != 0 ? g_tune_nslab : plan->nslab, g_tune_stream_c != 0);
         if (rc != MASK_OK) return rc;
@@ -404,9 +412,13 @@ extern "C" int mask_spmm_kernel_name(const mask_plan* plan, int format, int32_t 
     static const char* const fmt_name[] = {"srbcrs", "metcf", "mco"};
     if (format == kFmtSrbcrs && (epilogue & MASK_NUMERICS_TF32X3)) {
         snprintf(out, capacity, "spmm_async_kernel<tf32x3>");
+    } else if (format == kFmtSrbcrs && g_tune_sweep == 1 && N < 96 && g_tune_async != 0) {
+        snprintf(out, capacity, "spmm_async_kernel<%s>", fmt_name[format]);
     } else if (g_tune_sweep != 0) {
         int nslab = g_tune_nslab != 0 ? g_tune_nslab : plan->nslab;
-        if (nslab != 1 && nslab != 2 && nslab != 4) nslab = N > 256 ? 4 : (N > 128 ? 2 : 1);
+        const int fills = N > 256 ? 4 : (N > 128 ? 2 : 1);
+        if (nslab != 1 && nslab != 2 && nslab != 4) nslab = fills;
+        nslab = nslab < fills ? nslab : fills;
         const bool tma = g_tune_tma != 0 && format == kFmtSrbcrs && plan->d_vals_tf32 != nullptr;
         snprintf(out, capacity, "%s<nslab=%d,%s>", tma ? "spmm_tma_kernel" : "spmm_sweep_kernel", nslab, fmt_name[format]);
     } else {

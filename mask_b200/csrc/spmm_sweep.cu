@@ -478,7 +478,9 @@ static int launch_sweep_fmt(const mask_plan* plan, const SpmmArgs& a, cudaStream
 int launch_spmm_sweep(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int nslab) {
     if (a.N % 4 != 0) return fail(MASK_ERR_INVALID_ARGUMENT, "N must be a multiple of 4");
     if (plan->d_group_tile == nullptr) return fail(MASK_ERR_INVALID_ARGUMENT, "plan has no group tile table");
-    if (nslab != 1 && nslab != 2 && nslab != 4) nslab = a.N > 256 ? 4 : (a.N > 128 ? 2 : 1);
+    const int fills = a.N > 256 ? 4 : (a.N > 128 ? 2 : 1);   // slabs N can fill
+    if (nslab != 1 && nslab != 2 && nslab != 4) nslab = fills;
+    nslab = nslab < fills ? nslab : fills;
     SpmmArgs b = a;
     b.group_tile = plan->d_group_tile;
     b.n_groups = (int32_t)plan->G;

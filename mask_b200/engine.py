@@ -60,6 +60,15 @@ class Plan:
         check(lib().mask_plan_info(self._h, C.byref(f), C.byref(g), C.byref(p), C.byref(gt)), "mask_plan_info")
         return dict(fragments=f.value, groups=g.value, partial=p.value, group_tiles=gt.value)
 
+    def column_features(self) -> dict | None:
+        """What mask_plan_autotune measured and chose (None if it has not run)."""
+        f, ns = _lib.ColumnFeatures(), C.c_int32(0)
+        if lib().mask_plan_column_features(self._h, C.byref(f), C.byref(ns)) != 0:
+            return None
+        d = f.as_dict()
+        d["nslab_wide"] = int(ns.value)
+        return d
+
     def status(self) -> int:
         """Device status word: non-zero if a kernel using this plan gave up on a bounded wait."""
         v = C.c_int32(0)
@@ -116,11 +125,13 @@ class PackedSRBCRS:
             self.plans[key] = self.new_plan(policy, group_tiles)
         return self.plans[key]
 
-    def new_plan(self, policy: str = "auto", group_tiles: int = 0, prepare: bool = True) -> Plan:
-        """A plan for this matrix; carries the row map when the rows were reordered and, for SR-BCRS,
-        the rounded copy of the tile values that the TMA-fed kernel reads (``prepare``; costs as much
-        device memory as val_block_val again)."""
+    def new_plan(self, policy: str = "auto", group_tiles: int = 0, prepare: bool = False, autotune: bool = True) -> Plan:
+        """A plan for this matrix: tuned from the matrix's column features (``autotune``), carrying the
+        row map when the rows were reordered and, on request, the rounded copy of the tile values that
+        the TMA-fed kernel reads (``prepare``; as much device memory as val_block_val again)."""
         p = Plan(self.val_soff, self.M, self.T, policy, group_tiles)
+        if autotune and self.T > 0:
+            check(lib().mask_plan_autotune(p._h, _ptr(self.val_soff), _ptr(self.val_sidx), self.K, _stream()), "mask_plan_autotune")
         if prepare and isinstance(self, PackedSRBCRS) and self.T > 0:
             check(lib().mask_plan_prepare_values(p._h, _ptr(self.val_block_val), _stream()), "mask_plan_prepare_values")
         if self.row_order is not None:
@@ -192,14 +203,13 @@ def _analyze(rowptr, colind, M, K):
 
 def reorder_rows(rowptr, colind, M: int, K: int, kind: str) -> torch.Tensor:
     """Row order of one of the Format-DSL bridge's reorders (``row_rcm``, ``first_col_sort``,
-    ``jaccard_greedy``), computed on the host like the bridge does; returns order[new] = original
-    as an int32 tensor on the CSR's device."""
+    ``jaccard_greedy``), computed on the device; returns order[new] = original as an int32 tensor
+    on the CSR's device."""
     _req(rowptr, torch.int32, "rowptr")
     _req(colind, torch.int32, "colind")
-    rp, ci = rowptr.cpu(), colind.cpu()
-    order = torch.empty(M, dtype=torch.int32)
-    check(lib().mask_reorder_rows(_lib.REORDER[kind], _ptr(rp), _ptr(ci), M, K, _ptr(order)), "mask_reorder_rows")
-    return order.to(rowptr.device)
+    order = torch.empty(M, dtype=torch.int32, device=rowptr.device)
+    check(lib().mask_reorder_rows(_lib.REORDER[kind], _ptr(rowptr), _ptr(colind), M, K, _ptr(order), _stream()), "mask_reorder_rows")
+    return order
 
 
 def permute_rows(rowptr, colind, values, M: int, order: torch.Tensor):

@@ -102,5 +102,20 @@ def run_SRBCRS_16x8_multi_binding(dense, row_window_offset, tcblocktile_id, tcbl
     return run(_cache, dense, row_window_offset, num_nodes, "multi_bind")
 
 
+# The router's balance call (SPARSENE_SRBCRS_BALANCE=1) passes no num_edges and looks for these
+# spellings first (end2end/gcn/external_backend_spmm.py:737-763); without them it would pick the
+# eight-argument functions above and fail on the argument count.
+def run_SRBCRS_16x8_strict_lb_balance(dense, row_window_offset, tcblocktile_id, tcblock_offset, sparse_a_to_x_idx, num_nodes,
+                                      exeplan):
+    _check_handles(tcblocktile_id, tcblock_offset, sparse_a_to_x_idx)
+    return run(_cache, dense, row_window_offset, num_nodes, "strict_lb")
+
+
+def run_SRBCRS_16x8_multi_binding_balance(dense, row_window_offset, tcblocktile_id, tcblock_offset, sparse_a_to_x_idx,
+                                          num_nodes, exeplan):
+    _check_handles(tcblocktile_id, tcblock_offset, sparse_a_to_x_idx)
+    return run(_cache, dense, row_window_offset, num_nodes, "multi_bind")
+
+
 def reset_cache():
     _cache.clear()

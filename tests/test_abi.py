@@ -103,30 +103,6 @@ def test_invalid_arguments_are_reported_not_raised():
         _lib.check(1, "demo")
 
 
-@pytest.mark.parametrize("name", cases.golden_names() + ["rmat10", "hub_rows", "stencil8", "all_empty"])
-def test_host_reorders_match_golden_and_oracle(oracle_mod, name):
-    """mask_reorder_rows against the fixtures made by the reference bridge and against the oracle."""
-    L = _lib.lib()
-    if name in cases.SMALL:
-        m, g = cases.SMALL[name](), {}
-    else:
-        m, g = cases.load_golden(name)
-    for kind in ("first_col_sort", "jaccard_greedy", "row_rcm"):
-        order = np.zeros(m.M, np.int32)
-        rc = L.mask_reorder_rows(_lib.REORDER[kind], m.rowptr.ctypes.data, m.colind.ctypes.data, m.M, m.K, order.ctypes.data)
-        if kind == "row_rcm" and m.M != m.K:
-            assert rc == 1
-            continue
-        assert rc == 0
-        assert np.array_equal(order, oracle_mod.reorder_rows(kind, m.M, m.K, m.rowptr, m.colind)), kind
-        if "order_" + kind in g:
-            assert np.array_equal(order, g["order_" + kind]), kind
-    ident = np.zeros(m.M, np.int32)
-    assert L.mask_reorder_rows(0, m.rowptr.ctypes.data, m.colind.ctypes.data, m.M, m.K, ident.ctypes.data) == 0
-    assert np.array_equal(ident, np.arange(m.M))
-    assert L.mask_reorder_rows(9, m.rowptr.ctypes.data, m.colind.ctypes.data, m.M, m.K, ident.ctypes.data) == 1
-
-
 def _write_checkpoint(L, path, M, packed):
     return L.mask_metcf_checkpoint_write(path.encode(), M, packed["T"], packed["nnz_pad"], packed["val_soff"].ctypes.data,
                                          packed["val_sidx"].ctypes.data, packed["val_coo_off"].ctypes.data,

@@ -15,7 +15,8 @@ EXT = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), 
 # names the reference router resolves, first match wins (external_backend_spmm.py:632-763, 420-480)
 SRBCRS_NAMES = ["preprocess_gpu", "preprocess_gpu_16x8", "run_SRBCRS", "run_SRBCRS_balance", "run_SRBCRS_16x8",
                 "run_SRBCRS_16x8_balance", "preprocess_gpu_16x8_strict_lb", "run_SRBCRS_16x8_strict_lb",
-                "preprocess_gpu_16x8_multi_binding", "run_SRBCRS_16x8_multi_binding"]
+                "preprocess_gpu_16x8_multi_binding", "run_SRBCRS_16x8_multi_binding",
+                "run_SRBCRS_16x8_strict_lb_balance", "run_SRBCRS_16x8_multi_binding_balance"]
 DTC_NAMES = ["preprocess_gpu", "run_DTCSpMM", "preprocess_gpu_strict_lb", "preprocess_gpu_multi_binding",
              "run_DTCSpMM_strict_lb", "run_DTCSpMM_multi_binding", "run_DTCSpMM_balance",
              "run_DTCSpMM_strict_lb_balance", "run_DTCSpMM_multi_binding_balance", "DTCSpMM_gcn"]

@@ -195,3 +195,106 @@ def test_generators_gpu_passes_are_exact(monkeypatch):
     for a, b in zip(got["gpu"], got["host"]):
         assert a.M == b.M and np.array_equal(a.rowptr, b.rowptr) and np.array_equal(a.colind, b.colind)
         assert np.array_equal(a.values.view(np.int32), b.values.view(np.int32))
+
+
+@pytest.mark.parametrize("name", cases.golden_names() + ["rmat10", "hub_rows", "stencil8", "all_empty", "uniform512", "rmat12u",
+                                                         "m33_empty_window", "wide_k"])
+def test_device_reorders_match_golden_and_oracle(oracle_mod, name):
+    """mask_reorder_rows (device kernels: radix sorts, one block per Jaccard bucket, level-synchronous
+    Cuthill-McKee over all components) against the fixtures made by the reference bridge and against
+    the oracle's sequential restatement: the permutations must be identical."""
+    import torch
+    from mask_b200 import _lib, engine
+    L = _lib.lib()
+    if name in cases.SMALL:
+        m, g = cases.SMALL[name](), {}
+    else:
+        m, g = cases.load_golden(name)
+    rp, ci, _ = _dev(m)
+    for kind in ("first_col_sort", "jaccard_greedy", "row_rcm"):
+        if kind == "row_rcm" and m.M != m.K:
+            with pytest.raises(_lib.MaskError):
+                engine.reorder_rows(rp, ci, m.M, m.K, kind)
+            continue
+        order = engine.reorder_rows(rp, ci, m.M, m.K, kind).cpu().numpy()
+        assert np.array_equal(np.sort(order), np.arange(m.M)), kind          # a permutation
+        assert np.array_equal(order, oracle_mod.reorder_rows(kind, m.M, m.K, m.rowptr, m.colind)), kind
+        if "order_" + kind in g:
+            assert np.array_equal(order, g["order_" + kind]), kind
+    assert np.array_equal(engine.reorder_rows(rp, ci, m.M, m.K, "none").cpu().numpy(), np.arange(m.M))
+    bad = torch.zeros(m.M, dtype=torch.int32, device="cuda")
+    assert L.mask_reorder_rows(9, rp.data_ptr(), ci.data_ptr(), m.M, m.K, bad.data_ptr(), None) == 1
+
+
+def test_device_reorders_on_a_power_law_graph(oracle_mod):
+    """2^16 nodes, hub rows with thousands of entries, thousands of isolated nodes and small
+    components: every order equals the sequential one."""
+    from mask_b200 import engine, generators as G
+    m, _ = G.make_workload("rmat20_gcn", scale=16)
+    rp, ci, _ = _dev(m)
+    for kind in ("first_col_sort", "jaccard_greedy", "row_rcm"):
+        order = engine.reorder_rows(rp, ci, m.M, m.K, kind).cpu().numpy()
+        assert np.array_equal(order, oracle_mod.reorder_rows(kind, m.M, m.K, m.rowptr, m.colind)), kind
+
+
+def test_column_features_match_numpy():
+    """mask_features_columns (device: histogram of gathered ids, radix sort, prefix sums) against the
+    same quantities from NumPy on the packed ids."""
+    import ctypes as C
+    import torch
+    from mask_b200 import _lib, engine
+    L = _lib.lib()
+    m = cases.SMALL["rmat12u"]()
+    rp, ci, va = _dev(m)
+    p = engine.pack_srbcrs(rp, ci, va, m.M, m.K)
+    f = _lib.ColumnFeatures()
+    N = 512
+    _lib.check(L.mask_features_columns(p.val_soff.data_ptr(), p.val_sidx.data_ptr(), m.M, m.K, p.T, N, C.byref(f),
+                                       C.c_void_p(torch.cuda.current_stream().cuda_stream)), "mask_features_columns")
+    sidx = p.val_sidx.cpu().numpy().astype(np.int64)
+    soff = p.val_soff.cpu().numpy().astype(np.int64)
+    assert f.gathers == 8 * p.T == sidx.size
+    counts = np.bincount(sidx, minlength=m.K)
+    assert f.distinct_columns == int((counts > 0).sum())
+    top = np.sort(counts)[::-1].cumsum()
+    for i, width in enumerate((512, 256, 128)):
+        rows = min(m.K, max(1, (f.l2_bytes // 2) // (min(N, width) * 4)))
+        assert f.hub_columns[i] == rows
+        assert abs(f.hub_share[i] - top[rows - 1] / sidx.size) < 1e-12
+    win = np.repeat(np.arange(soff.size - 1), np.diff(soff))          # window of every tile
+    diag = np.repeat(win, 8) * 16 * m.K // m.M
+    d = np.abs(sidx - diag)
+    bucket = np.where(d == 0, 0, np.floor(np.log2(np.maximum(d, 1))).astype(np.int64) + 1)
+    hist = np.bincount(bucket, minlength=33).cumsum()
+    for q, got in ((0.5, f.band_p50), (0.9, f.band_p90)):
+        b = int(np.searchsorted(hist, q * sidx.size, side="left"))
+        assert got == (0 if b == 0 else min(1 << b, m.K))
+
+
+def test_plan_table_tells_a_stencil_from_a_power_law_graph():
+    """The plan table is keyed on matrix features: a 27-point stencil keeps its gathers within a narrow
+    band (4 slabs per sweep: tile values read once), a large power-law graph does not and gains from
+    narrower rows of B (2 slabs).  Both plans must still multiply correctly."""
+    import torch
+    from mask_b200 import engine, generators as G
+    st = G.stencil27(grid=40)
+    pl, _ = G.make_workload("rmat20_gcn", scale=19)
+    plans = {}
+    for name, m in (("stencil", st), ("power_law", pl)):
+        rp, ci, va = _dev(m)
+        p = engine.pack_srbcrs(rp, ci, va, m.M, m.K)
+        plan = p.new_plan("auto")
+        f = plan.column_features()
+        assert f is not None and f["gathers"] == 8 * p.T
+        plans[name] = (f, engine.kernel_signature(p, 512, plan)[0])
+        B = torch.randn((m.K, 512), device="cuda")
+        out = engine.spmm(p, B, plan=plan)
+        ref = torch.sparse.mm(torch.sparse_csr_tensor(rp.long(), ci.long(), va, size=(m.M, m.K)), B)
+        assert plan.status() == 0
+        assert float((out - ref).abs().max()) <= 2e-2 * float(ref.abs().max())
+    fs, ks = plans["stencil"]
+    fp, kp = plans["power_law"]
+    assert fs["band_p90"] * 16 < fp["band_p90"]                      # local against scattered gathers
+    assert fs["nslab_wide"] == 4 and "nslab=4" in ks
+    assert fp["nslab_wide"] == 2 and "nslab=2" in kp
+    assert fp["hub_share"][1] > fp["hub_share"][0] + 0.02

@@ -302,6 +302,7 @@ def test_srbcrs_spmm_tcgen05_kernel(oracle_mod, name, N, gt, nslab):
     pm = engine.pack_metcf(rp, ci, va, m.M, m.K)
     pc = engine.pack_mco(rp, ci, va, m.M, m.K)
     try:
+        engine.tune("sweep", 2)      # also for narrow N, where the library would pick the warp-level kernel
         engine.tune("nslab", nslab)
         engine.tune("stream_c", nslab == 2)
         out = torch.full((m.M, N), float("nan"), device="cuda")
@@ -314,13 +315,14 @@ def test_srbcrs_spmm_tcgen05_kernel(oracle_mod, name, N, gt, nslab):
         engine.spmm(pc, Bd, out=out4, plan=plan)
         # the TMA-fed kernel: a plan that holds the rounded tile values
         engine.tune("tma", 1)
-        plan_t = p.new_plan("auto", gt)
+        plan_t = p.new_plan("auto", gt, prepare=True)
         assert engine.kernel_signature(p, N, plan_t)[0].startswith("spmm_tma_kernel") or p.T == 0
         out5 = torch.full((m.M, N), float("nan"), device="cuda")
         engine.spmm(p, Bd, out=out5, plan=plan_t)
         out6 = torch.full((m.M, N), float("nan"), device="cuda")
         engine.spmm(p, Bd, out=out6, plan=plan_t, relu=True)
     finally:
+        engine.tune("sweep", 1)
         engine.tune("nslab", 0)
         engine.tune("stream_c", 0)
         engine.tune("tma", 0)
