@@ -520,10 +520,9 @@ def main():
     ap.add_argument("--format", default="srbcrs", choices=["srbcrs", "metcf", "mco"])
     ap.add_argument("--policy", default="auto")
     ap.add_argument("--group-tiles", type=int, default=0)
-    ap.add_argument("--hints", type=int, default=0, help="kernel variant: L2 eviction hints bitmask")
     ap.add_argument("--session-chunk", type=int, default=-1, help="columns per chunk of the host-buffer pipeline (-1 automatic, 0 off)")
-    ap.add_argument("--umma-variant", type=int, default=0, help="tcgen05 kernel: 0 = slabs by N, 1/2/3 = 128-column slabs (4/2/1 tiles per step), 4 = 256-column slabs")
-    ap.add_argument("--umma", type=int, default=1, help="1 = tcgen05 / tensor-memory kernel where it applies, 0 = mma.sync kernels")
+    ap.add_argument("--sweep", type=int, default=1, help="1 = tcgen05 kernel except where the warp-level one measures faster, 2 = always, 0 = warp-level kernels only")
+    ap.add_argument("--nslab", type=int, default=0, help="tcgen05 kernel: 128-column slabs per sweep (0 = the plan table's choice)")
     ap.add_argument("--e2e-steps", type=int, default=3, help="0 skips the host-buffer leg")
     ap.add_argument("--nq", type=int, default=0, help="kernel variant: 32-column groups per warp (0 = default)")
     ap.add_argument("--min-blocks", type=int, default=0, help="kernel variant: occupancy target (0 = default)")
@@ -560,9 +559,8 @@ def main():
     engine.tune("nq", args.nq)
     engine.tune("min_blocks", args.min_blocks)
     engine.tune("stages", args.stages)
-    engine.tune("hints", args.hints)
-    engine.tune("umma", args.umma)
-    engine.tune("umma_variant", args.umma_variant)
+    engine.tune("sweep", args.sweep)
+    engine.tune("nslab", args.nslab)
     engine.tune("session_chunk", args.session_chunk)
     engine.tune("async", 0 if args.no_async else 1)
 

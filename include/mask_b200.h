@@ -355,14 +355,14 @@ int mask_spmm_srbcrs_static_scratch(const mask_plan* plan, const int32_t* d_val_
                                     int32_t M, int32_t K, int32_t N, const float* d_B, int64_t ldb,
                                     float* d_C, int64_t ldc, int epilogue, void* stream);
 
-/* Development knobs for kernel variants, process-wide: "nq" (32-column groups per warp: 1, 2, 4;
- * 0 = chosen from N), "min_blocks" (occupancy target of the variant; 0 = default), "async" (0 =
- * register-pipelined kernel instead of the cp.async ring), "stages" (ring depth variant), "hints"
- * (bit 0: L2 eviction priorities, bit 1: streaming stores of C, bit 2: skip the rounding of tile
- * values), "umma" (0 = never the tcgen05 kernel, 1 = where it wins, 2 = wherever it fits),
- * "umma_variant" (0 = slabs by N, 1/2/3 = 128-column slabs with 4/2/1 tiles per step, 4 =
- * 256-column slabs), "session_chunk" (columns per chunk of mask_session_spmm_host).  Replaces
- * the reference's tile_b environment switches SRBCRS_TILE_B / DTC_TILE_B
+/* Development knobs for kernel variants, process-wide: "sweep" (1 = persistent tcgen05 kernel except
+ * where the warp-level one measures faster (N < 96), 2 = always, 0 = warp-level kernels only),
+ * "nslab" (tcgen05 kernel: 128-column slabs per sweep, 1 / 2 / 4; 0 = the plan table's choice),
+ * "tma" (1 = the TMA-fed kernel for plans prepared with mask_plan_prepare_values), and for the
+ * warp-level kernels "nq" (32-column groups per warp: 1, 2, 4; 0 = chosen from N), "min_blocks"
+ * (occupancy target; 0 = default), "async" (0 = register-pipelined kernel instead of the cp.async
+ * ring), "stages" (ring depth); "session_chunk" (columns per chunk of mask_session_spmm_host).
+ * Replaces the reference's tile_b environment switches SRBCRS_TILE_B / DTC_TILE_B
  * (examples/src_fp32/sr_bcrs/testbed/SRBCRSSpMM_kernel.cu:435-475). */
 int mask_tune(const char* name, int value);
 

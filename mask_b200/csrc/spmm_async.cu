@@ -34,24 +34,6 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0 + %2], [%1 + %3], 16;\n" ::"r"(dst), "l"(src), "n"(DST_IMM), "n"(SRC_IMM)
                  : "memory");
 }
-// Same with an L2 eviction-priority policy (createpolicy): gathered rows of B are kept
-// (evict_last) while the streamed tile values and ids are marked evict_first.
-template <int DST_IMM, int SRC_IMM>
-__device__ __forceinline__ void cp_async16_hint(uint32_t dst, const void* src, uint64_t policy) {
-    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0 + %3], [%1 + %4], 16, %2;\n" ::"r"(dst), "l"(src), "l"(policy),
-                 "n"(DST_IMM), "n"(SRC_IMM)
-                 : "memory");
-}
-__device__ __forceinline__ uint64_t l2_policy_evict_last() {
-    uint64_t p;
-    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-    return p;
-}
-__device__ __forceinline__ uint64_t l2_policy_evict_first() {
-    uint64_t p;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
-    return p;
-}
 // Same with zero fill: when !valid no source byte is read and the 16 destination bytes are zeroed.
 template <int DST_IMM, int SRC_IMM>
 __device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, bool valid) {
@@ -78,19 +60,15 @@ struct AsyncLayout {
 // Copies of one tile's B rows, unrolled over the 32-column groups with immediate offsets.
 template <int NQ, bool GUARD, int Q = 0>
 struct CopyRows {
-    static __device__ __forceinline__ void run(uint32_t dst, const float* r0, const float* r1, const bool (&qok)[NQ],
-                                               uint64_t policy, bool hint) {
+    static __device__ __forceinline__ void run(uint32_t dst, const float* r0, const float* r1, const bool (&qok)[NQ]) {
         if (GUARD) {
             cp_async16_zfill<Q * 1024, Q * 128>(dst, r0, qok[Q]);
             cp_async16_zfill<Q * 1024 + 512, Q * 128>(dst, r1, qok[Q]);
-        } else if (hint) {
-            cp_async16_hint<Q * 1024, Q * 128>(dst, r0, policy);
-            cp_async16_hint<Q * 1024 + 512, Q * 128>(dst, r1, policy);
         } else {
             cp_async16<Q * 1024, Q * 128>(dst, r0);
             cp_async16<Q * 1024 + 512, Q * 128>(dst, r1);
         }
-        if constexpr (Q + 1 < NQ) CopyRows<NQ, GUARD, Q + 1>::run(dst, r0, r1, qok, policy, hint);
+        if constexpr (Q + 1 < NQ) CopyRows<NQ, GUARD, Q + 1>::run(dst, r0, r1, qok);
     }
 };
 
@@ -140,9 +118,6 @@ __global__ void __launch_bounds__(WPB * 32, MIN_BLOCKS) spmm_async_kernel(const 
     const float* a_src = p.val_blk + (int64_t)t0 * kTileElems + lane * 4;
     const int* i_src = p.val_sidx + (int64_t)t0 * kTileCols + (lane & 1) * 4;
 
-    const bool hint = (p.hints & 1) != 0;
-    const uint64_t keep = l2_policy_evict_last();
-    const uint64_t stream = l2_policy_evict_first();
 
     float acc[NQ][4][4];
 #pragma unroll
@@ -163,10 +138,8 @@ __global__ void __launch_bounds__(WPB * 32, MIN_BLOCKS) spmm_async_kernel(const 
             const char* r0 = Bcol + (uint64_t)(uint32_t)id[lr] * ldb_bytes;
             const char* r1 = Bcol + (uint64_t)(uint32_t)id[lr + 4] * ldb_bytes;
             const uint32_t dst = ring_s + slot;
-            CopyRows<NQ, GUARD>::run(dst + cp_off, reinterpret_cast<const float*>(r0), reinterpret_cast<const float*>(r1), qok,
-                                     keep, hint);
-            if (hint) cp_async16_hint<L::kBBytes, 0>(dst + lane * 16, a_src + tt * kTileElems, stream);
-            else cp_async16<L::kBBytes, 0>(dst + lane * 16, a_src + tt * kTileElems);
+            CopyRows<NQ, GUARD>::run(dst + cp_off, reinterpret_cast<const float*>(r0), reinterpret_cast<const float*>(r1), qok);
+            cp_async16<L::kBBytes, 0>(dst + lane * 16, a_src + tt * kTileElems);
         }
     };
     auto next = [](int x, int step, int wrap) { x += step; return x == wrap ? 0 : x; };

@@ -34,7 +34,6 @@ struct SpmmArgs {
     int32_t N;
     int32_t relu;
     int32_t tf32x3;  // compensated products (MASK_NUMERICS_TF32X3)
-    int32_t hints;   // bit 0: L2 eviction-priority hints on the copies, bit 1: streaming stores of C
 };
 
 __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -123,13 +122,8 @@ __device__ __forceinline__ void flush_fragment(const SpmmArgs& p, int ff, int co
             }
             if (r < rows_ok) {
                 float* row = (slot < 0 && p.row_map) ? p.C + (int64_t)p.row_map[w * kWinRows + r] * p.ldc : dst + (int64_t)r * ld;
-                if (p.hints & 2) {  // C is written once and not read again by this kernel
-                    if (c0 < p.N) __stcs(reinterpret_cast<float4*>(row + c0), v0);
-                    if (c0 + 4 < p.N) __stcs(reinterpret_cast<float4*>(row + c0 + 4), v1);
-                } else {
-                    if (c0 < p.N) *reinterpret_cast<float4*>(row + c0) = v0;
-                    if (c0 + 4 < p.N) *reinterpret_cast<float4*>(row + c0 + 4) = v1;
-                }
+                if (c0 < p.N) *reinterpret_cast<float4*>(row + c0) = v0;
+                if (c0 + 4 < p.N) *reinterpret_cast<float4*>(row + c0 + 4) = v1;
                 if (slot < 0) {  // the same row into every peer's copy of C (plain stores over NVLink)
                     const int64_t off = row - p.C;
                     for (int j = 0; j < p.n_peer_out; j++) {
@@ -147,11 +141,6 @@ __device__ __forceinline__ void flush_fragment(const SpmmArgs& p, int ff, int co
     }
 }
 
-// spmm_umma.cu: tcgen05 / tensor-memory variant (SR-BCRS, N % 128 == 0, groups of at most
-// kUmmaMaxGroupTiles tiles).
-constexpr int kUmmaMaxGroupTiles = 256;
-int launch_spmm_umma(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int variant);
-
 // spmm_sweep.cu: persistent tcgen05 kernel, any N % 4 == 0, groups of any length.  nslab = 128-column
 // slabs per column block (1, 2, 4; 0 = by N).
 int launch_spmm_sweep(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int nslab);
@@ -159,7 +148,7 @@ int launch_spmm_sweep(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st,
 // spmm_tma.cu: persistent tcgen05 kernel fed by the tensor memory accelerator (SR-BCRS with a prepared
 // plan, see mask_plan_prepare_values).
 bool spmm_tma_applies(const mask_plan* plan, const SpmmArgs& a);
-int launch_spmm_tma(const mask_plan* plan, const SpmmArgs& a, int64_t K, cudaStream_t st, int nslab, bool stream_c);
+int launch_spmm_tma(const mask_plan* plan, const SpmmArgs& a, int64_t K, cudaStream_t st, int nslab);
 
 // spmm_async.cu: shared-memory ring variant (SR-BCRS).  nq / stages 0 = defaults.
 int launch_spmm_async(const mask_plan* plan, const SpmmArgs& a, cudaStream_t st, int nq, int stages);

@@ -40,13 +40,9 @@ static int g_tune_nq = 0;
 static int g_tune_min_blocks = 0;
 static int g_tune_async = 1;   // 1 = shared-memory ring fed by cp.async (SR-BCRS), 0 = register pipeline
 static int g_tune_stages = 0;
-static int g_tune_hints = 0;
 extern int g_session_chunk_cols;      // api.cu: column chunks of the host-buffer pipeline
-static int g_tune_umma_variant = 0;   // 0 = slabs by N, 1 / 2 = 128-column slabs with 4 / 2 tiles per step
-static int g_tune_umma = 1;    // 1 = tcgen05 kernel where it applies (see launch_spmm), 2 = whenever N % 128 == 0
-static int g_tune_sweep = 1;   // 1 = persistent tcgen05 kernel (spmm_sweep.cu) for every product but the compensated ones
+static int g_tune_sweep = 1;   // 1 = persistent tcgen05 kernel except where the warp-level one measures faster, 2 = always, 0 = warp-level kernels only
 static int g_tune_nslab = 0;   // persistent kernel: 128-column slabs per column block (0 = the plan's choice)
-static int g_tune_stream_c = 0;
 static int g_tune_tma = 0;     // 1 = the TMA-fed kernel where the plan holds rounded tile values (spmm_tma.cu); measured slower, off by default
 
 template <int NQ, int FMT, int MIN_BLOCKS>
@@ -321,11 +317,6 @@ static int launch_spmm(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
     // columns per warp: wide slabs (fewer re-reads of the tile values per column) when N fills
     // four warps of them, else narrower slabs so that small N still spreads over a block
     const int N = a.N;
-    a.hints = g_tune_hints;
-    // tcgen05 kernel: wins when a block covers 512 columns (4 slabs share one tile fetch and one
-    // pipeline step); with 1-2 slabs the mma.sync ring kernel is 10-30 % faster for SR-BCRS, while
-    // for ME-TCF it beats the register-pipelined kernel at every width.  umma = 2 forces it.
-    const bool umma_fits = N % 128 == 0 && plan->max_group_tiles <= kUmmaMaxGroupTiles;
     constexpr bool METCF = FMT != kFmtSrbcrs;   // the COO and bitmap leaves take the same routes
     if (FMT == kFmtSrbcrs && a.tf32x3) {   // compensated products: mma.sync ring kernel
         int rc = launch_spmm_async(plan, a, st, 0, 0);
@@ -341,17 +332,12 @@ static int launch_spmm(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
         return launch_fixup(plan, a, st);
     }
     if (g_tune_sweep != 0 && g_tune_tma != 0 && FMT == kFmtSrbcrs && spmm_tma_applies(plan, a)) {
-        int rc = launch_spmm_tma(plan, a, a.K, st, g_tune_nslab != 0 ? g_tune_nslab : plan->nslab, g_tune_stream_c != 0);
+        int rc = launch_spmm_tma(plan, a, a.K, st, g_tune_nslab != 0 ? g_tune_nslab : plan->nslab);
         if (rc != MASK_OK) return rc;
         return launch_fixup(plan, a, st);
     }
     if (g_tune_sweep != 0) {
         int rc = launch_spmm_sweep(plan, a, st, g_tune_nslab != 0 ? g_tune_nslab : plan->nslab);
-        if (rc != MASK_OK) return rc;
-        return launch_fixup(plan, a, st);
-    }
-    if (umma_fits && (g_tune_umma == 2 || (g_tune_umma == 1 && (METCF || N % 512 == 0)))) {
-        int rc = launch_spmm_umma(plan, a, st, g_tune_umma_variant);
         if (rc != MASK_OK) return rc;
         return launch_fixup(plan, a, st);
     }
@@ -434,12 +420,8 @@ extern "C" int mask_tune(const char* name, int value) {
     else if (!strcmp(name, "min_blocks")) g_tune_min_blocks = value;
     else if (!strcmp(name, "async")) g_tune_async = value;
     else if (!strcmp(name, "stages")) g_tune_stages = value;
-    else if (!strcmp(name, "hints")) g_tune_hints = value;
-    else if (!strcmp(name, "umma")) g_tune_umma = value;
-    else if (!strcmp(name, "umma_variant")) g_tune_umma_variant = value;
     else if (!strcmp(name, "sweep")) g_tune_sweep = value;
     else if (!strcmp(name, "nslab")) g_tune_nslab = value;
-    else if (!strcmp(name, "stream_c")) g_tune_stream_c = value;
     else if (!strcmp(name, "tma")) g_tune_tma = value;
     else if (!strcmp(name, "session_chunk")) g_session_chunk_cols = value;
     else return fail(MASK_ERR_INVALID_ARGUMENT, "unknown tuning knob");

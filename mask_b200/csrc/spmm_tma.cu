@@ -81,7 +81,7 @@ __device__ __forceinline__ bool mbar_wait_clock_only(uint32_t bar, uint32_t pari
     return true;
 }
 
-template <int NSLAB, bool STREAM_C>
+template <int NSLAB>
 __global__ void __launch_bounds__(kTmaThreads, 2) spmm_tma_kernel(const SpmmArgs p, const __grid_constant__ CUtensorMap bmap,
                                                                    const float* __restrict__ vals_tf32, int32_t* status) {
     using L = TmaLayout<NSLAB>;
@@ -319,8 +319,7 @@ __global__ void __launch_bounds__(kTmaThreads, 2) spmm_tma_kernel(const SpmmArgs
 #pragma unroll
                             for (int sl = 0; sl < NSLAB; sl++) {
                                 if (colok[sl]) {
-                                    if (STREAM_C) __stcs(rowp + 128 * sl, __uint_as_float(v[sl][i]));
-                                    else rowp[128 * sl] = __uint_as_float(v[sl][i]);
+                                    rowp[128 * sl] = __uint_as_float(v[sl][i]);
                                 }
                             }
                         }
@@ -384,11 +383,11 @@ static int make_b_map(CUtensorMap* map, const float* B, int64_t K, int32_t N, in
     return MASK_OK;
 }
 
-template <int NSLAB, bool STREAM_C>
+template <int NSLAB>
 static int launch_tma_variant(const mask_plan* plan, SpmmArgs a, const CUtensorMap& map, cudaStream_t st) {
     using L = TmaLayout<NSLAB>;
     static_assert(2 * (L::kDynamicBytes + 1024) <= 228 * 1024, "two blocks per SM");
-    auto kern = spmm_tma_kernel<NSLAB, STREAM_C>;
+    auto kern = spmm_tma_kernel<NSLAB>;
     MASK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));   // per device
     MASK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     // two blocks per SM by construction (shared memory asserted above; tensor memory at most 256 of 512 columns per block)
@@ -409,8 +408,10 @@ bool spmm_tma_applies(const mask_plan* plan, const SpmmArgs& a) {
            a.N >= 32 && a.ldb % 4 == 0 && (reinterpret_cast<uintptr_t>(a.B) & 15) == 0 && encode_tiled_fn() != nullptr;
 }
 
-int launch_spmm_tma(const mask_plan* plan, const SpmmArgs& a, int64_t K, cudaStream_t st, int nslab, bool stream_c) {
-    if (nslab != 1 && nslab != 2 && nslab != 4) nslab = a.N > 256 ? 4 : (a.N > 128 ? 2 : 1);
+int launch_spmm_tma(const mask_plan* plan, const SpmmArgs& a, int64_t K, cudaStream_t st, int nslab) {
+    const int fills = a.N > 256 ? 4 : (a.N > 128 ? 2 : 1);   // slabs N can fill
+    if (nslab != 1 && nslab != 2 && nslab != 4) nslab = fills;
+    nslab = nslab < fills ? nslab : fills;
     CUtensorMap map;
     int rc = make_b_map(&map, a.B, K, a.N, a.ldb);
     if (rc != MASK_OK) return rc;
@@ -418,14 +419,9 @@ int launch_spmm_tma(const mask_plan* plan, const SpmmArgs& a, int64_t K, cudaStr
     b.group_tile = plan->d_group_tile;
     b.n_groups = (int32_t)plan->G;
     b.n_frag = plan->F;
-    if (stream_c) {
-        if (nslab == 1) return launch_tma_variant<1, true>(plan, b, map, st);
-        if (nslab == 2) return launch_tma_variant<2, true>(plan, b, map, st);
-        return launch_tma_variant<4, true>(plan, b, map, st);
-    }
-    if (nslab == 1) return launch_tma_variant<1, false>(plan, b, map, st);
-    if (nslab == 2) return launch_tma_variant<2, false>(plan, b, map, st);
-    return launch_tma_variant<4, false>(plan, b, map, st);
+    if (nslab == 1) return launch_tma_variant<1>(plan, b, map, st);
+    if (nslab == 2) return launch_tma_variant<2>(plan, b, map, st);
+    return launch_tma_variant<4>(plan, b, map, st);
 }
 
 // ---- the rounded copy of the tile values --------------------------------------------------------------

@@ -95,14 +95,14 @@ def test_srbcrs_spmm_kernel_variants(oracle_mod, name, N, use_async, nq, knob):
     p = engine.pack_srbcrs(rp, ci, va, m.M, m.K)
     B = _dense(m.K, N, 9)
     try:
-        engine.tune("umma", 0)
+        engine.tune("sweep", 0)
         engine.tune("async", use_async)
         engine.tune("nq", nq)
         engine.tune("stages" if use_async else "min_blocks", knob)
         out = torch.full((m.M, N), float("nan"), device="cuda")
         engine.spmm(p, torch.from_numpy(B).cuda(), out=out, plan=engine.Plan(p.val_soff, m.M, p.T, "auto", 3))
     finally:
-        engine.tune("umma", 1)
+        engine.tune("sweep", 1)
         engine.tune("async", 1)
         engine.tune("nq", 0)
         engine.tune("stages", 0)
@@ -129,10 +129,10 @@ def test_metcf_spmm_matches_oracle(oracle_mod, name, N):
     _assert_close(oracle_mod, m, B, out2.cpu().numpy())
     assert plan2.status() == 0
     try:  # and the mma.sync ME-TCF kernel
-        engine.tune("umma", 0)
+        engine.tune("sweep", 0)
         out3 = engine.spmm(p, torch.from_numpy(B).cuda(), plan=plan2)
     finally:
-        engine.tune("umma", 1)
+        engine.tune("sweep", 1)
     _assert_close(oracle_mod, m, B, out3.cpu().numpy())
 
 
@@ -140,8 +140,8 @@ def test_metcf_spmm_matches_oracle(oracle_mod, name, N):
                                   "one_tile_windows", "uniform512"])
 @pytest.mark.parametrize("N", [40, 128, 256, 512])
 def test_mco_spmm_matches_oracle(oracle_mod, name, N):
-    """MCO / BIT-TCF (bitmap leaf): tcgen05 kernel for N % 128 == 0 in every slab variant, the
-    register-pipelined kernel otherwise, split windows, ReLU; and exactly the product the oracle
+    """MCO / BIT-TCF (bitmap leaf): tcgen05 kernel in its slab variants, the register-pipelined
+    kernel, split windows, ReLU; and exactly the product the oracle
     computes from the same arrays with both operands rounded."""
     import torch
     from mask_b200 import engine
@@ -159,15 +159,15 @@ def test_mco_spmm_matches_oracle(oracle_mod, name, N):
     assert plan2.status() == 0
     outs = []
     try:
-        for umma, variant in ((0, 0), (2, 1), (2, 3)):
-            engine.tune("umma", umma)
-            engine.tune("umma_variant", variant)
+        for sweep, nslab in ((0, 0), (2, 1), (2, 2)):   # warp-level kernels; tcgen05 with 1 and 2 slabs
+            engine.tune("sweep", sweep)
+            engine.tune("nslab", nslab)
             o = torch.full((m.M, N), float("nan"), device="cuda")
             engine.spmm(p, Bd, out=o, plan=plan2)
             outs.append(o)
     finally:
-        engine.tune("umma", 1)
-        engine.tune("umma_variant", 0)
+        engine.tune("sweep", 1)
+        engine.tune("nslab", 0)
     for o in outs:
         _assert_close(oracle_mod, m, B, o.cpu().numpy())
     assert plan2.status() == 0
@@ -304,7 +304,6 @@ def test_srbcrs_spmm_tcgen05_kernel(oracle_mod, name, N, gt, nslab):
     try:
         engine.tune("sweep", 2)      # also for narrow N, where the library would pick the warp-level kernel
         engine.tune("nslab", nslab)
-        engine.tune("stream_c", nslab == 2)
         out = torch.full((m.M, N), float("nan"), device="cuda")
         engine.spmm(p, Bd, out=out, plan=plan)
         out2 = torch.full((m.M, N), float("nan"), device="cuda")
@@ -324,7 +323,6 @@ def test_srbcrs_spmm_tcgen05_kernel(oracle_mod, name, N, gt, nslab):
     finally:
         engine.tune("sweep", 1)
         engine.tune("nslab", 0)
-        engine.tune("stream_c", 0)
         engine.tune("tma", 0)
     assert plan.status() == 0 and plan_t.status() == 0
     _assert_close(oracle_mod, m, B, out5.cpu().numpy())
@@ -336,12 +334,15 @@ def test_srbcrs_spmm_tcgen05_kernel(oracle_mod, name, N, gt, nslab):
 
 
 @pytest.mark.parametrize("name,N,gt,umma,fmt,reorder", [
-    ("rmat12u", 64, 0, 1, "srbcrs", "none"),       # cp.async ring kernel
+    ("rmat12u", 64, 0, 1, "srbcrs", "none"),       # narrow N: cp.async ring kernel (warp-level MMA)
     ("hub_rows", 64, 3, 1, "srbcrs", "none"),      # split windows: fix-up kernel writes the rows
-    ("rmat12u", 512, 0, 2, "srbcrs", "none"),      # tcgen05 kernel, 4 slabs
-    ("hub_rows", 128, 3, 2, "srbcrs", "none"),     # tcgen05 kernel + fix-up
-    ("m17", 40, 0, 1, "metcf", "none"),            # register kernel, ragged last window
+    ("rmat12u", 512, 0, 1, "srbcrs", "none"),      # tcgen05 kernel, 4 slabs
+    ("hub_rows", 128, 3, 1, "srbcrs", "none"),     # tcgen05 kernel + fix-up
+    ("hub_rows", 64, 3, 2, "srbcrs", "none"),      # tcgen05 kernel forced at narrow N
+    ("m17", 40, 0, 0, "metcf", "none"),            # register kernel, ragged last window
+    ("m17", 40, 0, 1, "metcf", "none"),            # tcgen05 kernel, ME-TCF
     ("rmat10", 64, 0, 1, "srbcrs", "row_rcm"),     # rows scattered back through the row map
+    ("rmat10", 256, 0, 1, "srbcrs", "row_rcm"),    # the same through the tcgen05 epilogue
 ])
 def test_peer_outputs_receive_the_same_rows(oracle_mod, name, N, gt, umma, fmt, reorder):
     """mask_plan_set_peer_outputs: every extra output base gets exactly the rows C gets (here the
@@ -362,14 +363,14 @@ def test_peer_outputs_receive_the_same_rows(oracle_mod, name, N, gt, umma, fmt, 
     peers = [torch.full((m.M, N), float("nan"), device="cuda") for _ in range(2)]
     ptrs = torch.tensor([t.data_ptr() for t in peers], dtype=torch.int64, device="cuda")
     try:
-        engine.tune("umma", umma)
+        engine.tune("sweep", umma)
         plan.set_peer_outputs(ptrs)
         engine.spmm(p, Bd, out=out, plan=plan, relu=True)
         plan.set_peer_outputs(None)
         plain = torch.full((m.M, N), float("nan"), device="cuda")
         engine.spmm(p, Bd, out=plain, plan=plan, relu=True)
     finally:
-        engine.tune("umma", 1)
+        engine.tune("sweep", 1)
     assert plan.status() == 0
     assert torch.equal(out, plain)
     for t in peers:
