@@ -184,6 +184,8 @@ typedef struct mask_column_features {
     int32_t hub_columns[3];   /* how many rows of B fit half the L2 at row widths of min(N,512), min(N,256), min(N,128) columns */
     double hub_share[3];      /* share of all gathers that go to that many most gathered columns */
     int32_t l2_bytes;
+    int32_t local_rows;       /* half-width of the band whose rows of B (min(N,512) columns wide) fill half the L2 */
+    double local_share;       /* share of all gathers within local_rows of their window's diagonal position */
 } mask_column_features;
 int mask_features_columns(const int32_t* d_val_soff, const int32_t* d_val_sidx, int32_t M, int32_t K, int64_t T,
                           int32_t N, mask_column_features* out, void* stream);

@@ -81,12 +81,12 @@ class Features(C.Structure):
 class ColumnFeatures(C.Structure):
     """mask_column_features"""
     _fields_ = [("gathers", i64), ("distinct_columns", i32), ("band_p50", i32), ("band_p90", i32), ("hub_columns", i32 * 3),
-                ("hub_share", C.c_double * 3), ("l2_bytes", i32)]
+                ("hub_share", C.c_double * 3), ("l2_bytes", i32), ("local_rows", i32), ("local_share", C.c_double)]
 
     def as_dict(self):
         return dict(gathers=int(self.gathers), distinct_columns=int(self.distinct_columns), band_p50=int(self.band_p50),
                     band_p90=int(self.band_p90), hub_columns=list(self.hub_columns), hub_share=[round(x, 4) for x in self.hub_share],
-                    l2_bytes=int(self.l2_bytes))
+                    l2_bytes=int(self.l2_bytes), local_rows=int(self.local_rows), local_share=round(float(self.local_share), 4))
 
 
 EPILOGUE_NONE, EPILOGUE_RELU = 0, 1

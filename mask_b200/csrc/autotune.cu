@@ -40,9 +40,10 @@ constexpr int kBandBuckets = 33;   // bucket b: distances in [2^(b-1), 2^b), buc
 
 // one thread per tile: window by binary search in val_soff, then its 8 ids
 __global__ void column_stats_kernel(const int32_t* __restrict__ soff, const int32_t* __restrict__ sidx, int32_t W, int64_t T,
-                                    int32_t M, int32_t K, uint32_t* __restrict__ counts, unsigned long long* __restrict__ band_hist) {
-    __shared__ unsigned int hist[kBandBuckets];
-    if (threadIdx.x < kBandBuckets) hist[threadIdx.x] = 0;
+                                    int32_t M, int32_t K, int64_t local_rows, uint32_t* __restrict__ counts,
+                                    unsigned long long* __restrict__ band_hist) {
+    __shared__ unsigned int hist[kBandBuckets + 1];   // last entry: gathers within local_rows of the diagonal
+    if (threadIdx.x <= kBandBuckets) hist[threadIdx.x] = 0;
     __syncthreads();
     const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (t < T) {
@@ -58,10 +59,11 @@ __global__ void column_stats_kernel(const int32_t* __restrict__ soff, const int3
             atomicAdd(&counts[id], 1u);
             const int64_t d = id > diag ? id - diag : diag - id;
             atomicAdd(&hist[d == 0 ? 0 : 64 - __clzll((unsigned long long)d)], 1u);
+            if (d <= local_rows) atomicAdd(&hist[kBandBuckets], 1u);
         }
     }
     __syncthreads();
-    if (threadIdx.x < kBandBuckets && hist[threadIdx.x]) atomicAdd(&band_hist[threadIdx.x], (unsigned long long)hist[threadIdx.x]);
+    if (threadIdx.x <= kBandBuckets && hist[threadIdx.x]) atomicAdd(&band_hist[threadIdx.x], (unsigned long long)hist[threadIdx.x]);
 }
 
 __global__ void count_nonzero_kernel(const uint32_t* __restrict__ counts, int32_t K, int32_t* __restrict__ out) {
@@ -97,14 +99,17 @@ extern "C" int mask_features_columns(const int32_t* d_val_soff, const int32_t* d
     int rc = counts.alloc((size_t)K * 4);
     if (rc == MASK_OK) rc = sorted.alloc((size_t)K * 4);
     if (rc == MASK_OK) rc = prefix.alloc((size_t)K * 8);
-    if (rc == MASK_OK) rc = hist.alloc(kBandBuckets * 8);
+    if (rc == MASK_OK) rc = hist.alloc((kBandBuckets + 1) * 8);
     if (rc == MASK_OK) rc = nz.alloc(16);
     if (rc != MASK_OK) return rc;
     MASK_CUDA_TRY(cudaMemsetAsync(counts.p, 0, (size_t)K * 4, st));
-    MASK_CUDA_TRY(cudaMemsetAsync(hist.p, 0, kBandBuckets * 8, st));
+    MASK_CUDA_TRY(cudaMemsetAsync(hist.p, 0, (kBandBuckets + 1) * 8, st));
     MASK_CUDA_TRY(cudaMemsetAsync(nz.p, 0, 16, st));
-    column_stats_kernel<<<(unsigned)((T + 255) / 256), 256, 0, st>>>(d_val_soff, d_val_sidx, W, T, M, K, counts.as<uint32_t>(),
-                                                                    hist.as<unsigned long long>());
+    // "local": a band of windows keeps rows of B alive that take at most half the L2 at this row width
+    const int width0 = std::min(N, 512);
+    out->local_rows = (int32_t)std::min<int64_t>(K, std::max<int64_t>(0, ((int64_t)(l2 / 2) / ((int64_t)width0 * 4) - kWinRows) / 2));
+    column_stats_kernel<<<(unsigned)((T + 255) / 256), 256, 0, st>>>(d_val_soff, d_val_sidx, W, T, M, K, (int64_t)out->local_rows,
+                                                                    counts.as<uint32_t>(), hist.as<unsigned long long>());
     count_nonzero_kernel<<<(unsigned)((K + 255) / 256), 256, 0, st>>>(counts.as<uint32_t>(), K, nz.as<int32_t>());
     MASK_CUDA_TRY(cudaGetLastError());
     // gathers per column, most gathered first, and their running sum
@@ -116,7 +121,7 @@ extern "C" int mask_features_columns(const int32_t* d_val_soff, const int32_t* d
     if (rc != MASK_OK) return rc;
     MASK_CUDA_TRY(cub::DeviceRadixSort::SortKeysDescending(tmp.p, b1, counts.as<uint32_t>(), sorted.as<uint32_t>(), K, 0, 32, st));
     MASK_CUDA_TRY(cub::DeviceScan::InclusiveSum(tmp.p, b2, as64, prefix.as<unsigned long long>(), K, st));
-    unsigned long long h[kBandBuckets];
+    unsigned long long h[kBandBuckets + 1];
     MASK_CUDA_TRY(cudaMemcpyAsync(h, hist.p, sizeof(h), cudaMemcpyDeviceToHost, st));
     MASK_CUDA_TRY(cudaMemcpyAsync(&out->distinct_columns, nz.p, 4, cudaMemcpyDeviceToHost, st));
     unsigned long long reach[3] = {0, 0, 0};
@@ -130,6 +135,7 @@ extern "C" int mask_features_columns(const int32_t* d_val_soff, const int32_t* d
     unsigned long long total = 0;
     for (int b = 0; b < kBandBuckets; b++) total += h[b];
     for (int i = 0; i < 3; i++) out->hub_share[i] = total ? (double)reach[i] / (double)total : 0.0;
+    out->local_share = total ? (double)h[kBandBuckets] / (double)total : 1.0;
     auto percentile = [&](double q) -> int32_t {
         unsigned long long run = 0;
         for (int b = 0; b < kBandBuckets; b++) {
@@ -158,10 +164,10 @@ extern "C" int mask_plan_autotune(mask_plan* plan, const int32_t* d_val_soff, co
     plan->col_features = f;
     plan->has_col_features = 1;
     const double half_l2 = 0.5 * (double)f.l2_bytes;
-    const double band_bytes = (2.0 * (double)f.band_p90 + kWinRows) * 4.0 * 512.0;   // rows of B a band of windows keeps alive
     const double b_bytes = (double)f.distinct_columns * 4.0 * 512.0;
-    const bool local = band_bytes <= half_l2 || b_bytes <= half_l2;
-    const bool narrower_rows_pay = !local && b_bytes > 8.0 * half_l2 && f.hub_share[1] - f.hub_share[0] >= 0.02;
+    const bool local = f.local_share >= 0.9 || b_bytes <= half_l2;   // the gathers stay near the diagonal, or all of B fits
+    // hub-heavy (a quarter of the gathers already fit at full width) and markedly more fits at half width
+    const bool narrower_rows_pay = !local && b_bytes > 8.0 * half_l2 && f.hub_share[0] >= 0.25 && f.hub_share[1] - f.hub_share[0] >= 0.02;
     plan->nslab = narrower_rows_pay ? 2 : 4;
     return MASK_OK;
 }

@@ -269,6 +269,8 @@ def test_column_features_match_numpy():
     for q, got in ((0.5, f.band_p50), (0.9, f.band_p90)):
         b = int(np.searchsorted(hist, q * sidx.size, side="left"))
         assert got == (0 if b == 0 else min(1 << b, m.K))
+    assert f.local_rows == min(m.K, max(0, ((f.l2_bytes // 2) // (512 * 4) - 16) // 2))
+    assert abs(f.local_share - float((d <= f.local_rows).mean())) < 1e-12
 
 
 def test_plan_table_tells_a_stencil_from_a_power_law_graph():
@@ -294,7 +296,7 @@ def test_plan_table_tells_a_stencil_from_a_power_law_graph():
         assert float((out - ref).abs().max()) <= 2e-2 * float(ref.abs().max())
     fs, ks = plans["stencil"]
     fp, kp = plans["power_law"]
-    assert fs["band_p90"] * 16 < fp["band_p90"]                      # local against scattered gathers
+    assert fs["band_p90"] * 16 < fp["band_p90"] and fs["local_share"] >= 0.9 > fp["local_share"]   # local against scattered gathers
     assert fs["nslab_wide"] == 4 and "nslab=4" in ks
     assert fp["nslab_wide"] == 2 and "nslab=2" in kp
     assert fp["hub_share"][1] > fp["hub_share"][0] + 0.02
