@@ -95,12 +95,18 @@ class Plan:
         return fo, fw[: i["fragments"]], go
 
     def scratch(self, N: int, device) -> torch.Tensor | None:
+        """Partial-tile buffer for the current stream: products on different streams may overlap on
+        the GPU, so each stream gets its own buffer (products on one stream run in order and share it)."""
         need = self.scratch_bytes(N)
         if need == 0:
             return None
-        if self._scratch is None or self._scratch.numel() < need or self._scratch.device != device:
-            self._scratch = torch.empty(need, dtype=torch.uint8, device=device)
-        return self._scratch
+        if self._scratch is None:
+            self._scratch = {}
+        key = (torch.cuda.current_stream().cuda_stream, device)
+        buf = self._scratch.get(key)
+        if buf is None or buf.numel() < need:
+            buf = self._scratch[key] = torch.empty(need, dtype=torch.uint8, device=device)
+        return buf
 
 
 @dataclass
