@@ -30,9 +30,10 @@
 // every quarter-warp reads one contiguous 128-byte line of B and writes one bank-conflict-free row of
 // the swizzled operand), copies the tile operand(s), and -- when it comes back four steps later --
 // waits for its own copies of the previous step (cp.async.wait_group), rounds the tile values to
-// TF32 in place (each lane the 16 bytes it copied itself; ME-TCF / MCO tiles are expanded here),
-// issues the fence.proxy.async that cp.async data needs before the tensor core may read it, and
-// signals ready[s].  Compared with splitting every step over all producer warps this costs a third
+// TF32 in place (each lane the 16 bytes it copied itself), issues the fence.proxy.async that
+// cp.async data needs before the tensor core may read it, and signals ready[s].  (ME-TCF and MCO
+// tiles have to be expanded from their stored form first; for them two more warps, 9-10, wait for a
+// step's copies on full[s], expand, fence and signal, 352 threads in all.)  Compared with splitting every step over all producer warps this costs a third
 // of the instructions (the per-step bookkeeping is paid by one warp, not four), needs no separate
 // preparation warps and no "landed" barrier, and the look-ahead of the column ids comes for free:
 // a warp loads the ids of its next step while it works on the current one.  Rings: ready[s]
@@ -49,7 +50,8 @@
 
 namespace mask {
 
-constexpr int kSweepThreads = 288;
+// 9 warps for SR-BCRS; the COO and bitmap leaves add two warps that expand the tiles (see below)
+constexpr int sweep_threads(int fmt) { return fmt == kFmtSrbcrs ? 288 : 352; }
 
 template <int NSLAB, int FMT>
 struct SweepLayout {
@@ -68,7 +70,7 @@ struct SweepLayout {
     static constexpr int kA = S * kStageB;
     static constexpr int kCoo = kA + S * kStageA;
     static constexpr int kBars = kCoo + ((S * KT * kCooStride + 15) & ~15);   // empty[S], ready[S], acc_full[NACC], acc_empty[NACC], drain
-    static constexpr int kNumBars = 2 * S + 2 * kNacc + 1;
+    static constexpr int kNumBars = 3 * S + 2 * kNacc + 1;   // empty, ready, full (expanding warps only), acc_full, acc_empty, drain
     static constexpr int kTmemSlot = kBars + kNumBars * 8;
     static constexpr int kAbort = kTmemSlot + 8;
     static constexpr int kBytes = kAbort + 8;
@@ -86,7 +88,7 @@ __device__ __forceinline__ bool mbar_wait_drain(uint32_t bar, uint32_t parity) {
 }
 
 template <int NSLAB, int FMT>
-__global__ void __launch_bounds__(kSweepThreads, 2) spmm_sweep_kernel(const SpmmArgs p, int32_t* status) {
+__global__ void __launch_bounds__(sweep_threads(FMT), 2) spmm_sweep_kernel(const SpmmArgs p, int32_t* status) {
     constexpr bool METCF = FMT == kFmtMetcf, MCO = FMT == kFmtMco;
     using L = SweepLayout<NSLAB, FMT>;
     constexpr int KT = L::KT, S = L::S, NACC = L::kNacc, kAccCols = L::kAccCols;
@@ -97,9 +99,15 @@ __global__ void __launch_bounds__(kSweepThreads, 2) spmm_sweep_kernel(const Spmm
     const uint32_t bars = base + L::kBars;
     auto empty_bar = [&](int s) { return bars + 8u * s; };
     auto ready_bar = [&](int s) { return bars + 8u * (S + s); };
-    auto accf_bar = [&](int b) { return bars + 8u * (2 * S + b); };
-    auto acce_bar = [&](int b) { return bars + 8u * (2 * S + NACC + b); };
-    const uint32_t drain_bar = bars + 8u * (2 * S + 2 * NACC);
+    auto full_bar = [&](int s) { return bars + 8u * (2 * S + s); };
+    auto accf_bar = [&](int b) { return bars + 8u * (3 * S + b); };
+    auto acce_bar = [&](int b) { return bars + 8u * (3 * S + NACC + b); };
+    const uint32_t drain_bar = bars + 8u * (3 * S + 2 * NACC);
+    // ME-TCF and MCO tiles are expanded from their stored form, which takes a few hundred cycles of
+    // dependent shared-memory work per tile: done by the producing warp itself that put the hand-over of a
+    // step behind the issue of the next one and made those encodings twice as slow as SR-BCRS, so they
+    // get two warps of their own that wait for a step's copies (full[s]) and hand it over.
+    constexpr bool kExpandWarps = FMT != kFmtSrbcrs;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + L::kAbort);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + L::kTmemSlot);
 
@@ -111,7 +119,8 @@ __global__ void __launch_bounds__(kSweepThreads, 2) spmm_sweep_kernel(const Spmm
         *abort_flag = 0;
         for (int s = 0; s < S; s++) {
             mbar_init(empty_bar(s), 1);    // tcgen05.commit
-            mbar_init(ready_bar(s), 1);    // lane 0 of the producing warp
+            mbar_init(ready_bar(s), 1);    // lane 0 of the warp that hands the step over
+            mbar_init(full_bar(s), 32);    // one deferred arrive per lane of the producing warp (expanding warps only)
         }
         for (int b = 0; b < NACC; b++) {
             mbar_init(accf_bar(b), 1);     // tcgen05.commit
@@ -138,7 +147,7 @@ __global__ void __launch_bounds__(kSweepThreads, 2) spmm_sweep_kernel(const Spmm
         return (cb & 1) ? G - 1 - gi : gi;
     };
 
-    if (warp >= 5) {
+    if (warp >= 5 && warp < 9) {
         // ------------------------------ producers (each warp owns every fourth step) -------------------
         const int pw = warp - 5;
         const int lr = lane >> 3, lc = lane & 7; // row (and row + 4), 16-byte chunk
@@ -149,37 +158,16 @@ __global__ void __launch_bounds__(kSweepThreads, 2) spmm_sweep_kernel(const Spmm
         int pend_s = -1, pend_cnt = 0;           // this warp's last step: copies issued, not yet handed to the MMA thread
         bool ok = true;
 
-        // Hands a landed step over: round / expand the tile operand(s), make the copies visible to the
+        // Hands a landed step over (SR-BCRS): round the tile operand(s), make the copies visible to the
         // tensor core's proxy, signal ready.
         auto finish = [&](int s, int cnt) {
 #pragma unroll
             for (int u = 0; u < KT; u++) {
-                if (u < cnt) {
-                    unsigned char* aslot = gbase + L::kA + s * L::kStageA + u * 512;
-                    if (METCF) {  // rebuild the 16x8 operand: zero, then tile[idx] = rna(value) over the run
-                        __syncwarp();   // the staged run was copied by other lanes
-                        const unsigned char* st = gbase + L::kCoo + (s * KT + u) * L::kCooStride;
-                        uint32_t* tile = reinterpret_cast<uint32_t*>(aslot);
-                        reinterpret_cast<uint4*>(tile)[lane] = make_uint4(0u, 0u, 0u, 0u);
-                        __syncwarp();
-                        const int2 run = *reinterpret_cast<const int2*>(st + L::kRunAt);
-                        const int rcnt = run.y - run.x;
-                        const int* sidx = reinterpret_cast<const int*>(st);
-                        const uint32_t* sval = reinterpret_cast<const uint32_t*>(st + 128);
-                        if (lane < rcnt) tile[sidx[lane]] = sval[lane] + 0x1000u;
-                        for (int e = run.x + 32 + lane; e < run.y; e += 32)   // dense tiles: entries beyond the staged 32
-                            tile[__ldg(p.coo_idx + e)] = __float_as_uint(__ldg(p.coo_val + e)) + 0x1000u;
-                    } else if (MCO) {
-                        __syncwarp();   // mask and values were copied by other lanes
-                        const unsigned char* st = gbase + L::kCoo + (s * KT + u) * L::kCooStride;
-                        const ulonglong2 m = *reinterpret_cast<const ulonglong2*>(st);
-                        reinterpret_cast<uint4*>(aslot)[lane] = mco_expand(m.x, m.y, reinterpret_cast<const uint32_t*>(st + 16), lane);
-                    } else {  // round the tile values to TF32 (nearest, ties away) in place: each lane its own 16 bytes
-                        uint4* at = reinterpret_cast<uint4*>(aslot) + lane;
-                        uint4 v = *at;
-                        v.x += 0x1000u; v.y += 0x1000u; v.z += 0x1000u; v.w += 0x1000u;
-                        *at = v;
-                    }
+                if (u < cnt) {  // round the tile values to TF32 (nearest, ties away) in place: each lane its own 16 bytes
+                    uint4* at = reinterpret_cast<uint4*>(gbase + L::kA + s * L::kStageA + u * 512) + lane;
+                    uint4 v = *at;
+                    v.x += 0x1000u; v.y += 0x1000u; v.z += 0x1000u; v.w += 0x1000u;
+                    *at = v;
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -281,17 +269,65 @@ __global__ void __launch_bounds__(kSweepThreads, 2) spmm_sweep_kernel(const Spmm
                         }
                     }
                 }
-                asm volatile("cp.async.commit_group;" ::: "memory");
-                if (pend_s >= 0) {   // the step this warp issued four steps ago has had that long to land
-                    asm volatile("cp.async.wait_group 1;" ::: "memory");
-                    finish(pend_s, pend_cnt);
+                if (kExpandWarps) {   // arrives on full[s] once every copy this lane has issued so far has landed
+                    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(full_bar(s)) : "memory");
+                } else {
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                    if (pend_s >= 0) {   // the step this warp issued four steps ago has had that long to land
+                        asm volatile("cp.async.wait_group 1;" ::: "memory");
+                        finish(pend_s, pend_cnt);
+                    }
+                    pend_s = s; pend_cnt = cnt;
                 }
-                pend_s = s; pend_cnt = cnt;
             }
             gstep += (uint32_t)n_steps;
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
         if (ok && pend_s >= 0) finish(pend_s, pend_cnt);
+    } else if (warp >= 9) {
+        // ------------------------------ expanding warps (ME-TCF / MCO only; alternate steps) -----------
+        const int q = warp - 9;
+        uint32_t gi = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            const int g = item_group(item, item_cb(item));
+            const int t0 = p.group_tile[g], t1 = p.group_tile[g + 1];
+            for (int tb = t0; tb < t1; tb += KT, gi++) {
+                // by stage, not by step: a barrier must be waited on in every one of its phases by the same
+                // waiter (with an odd ring a step-parity split would hand each warp every other phase of a
+                // stage, and a parity wait cannot tell phase k from phase k + 2)
+                const int s = (int)(gi % S);
+                if ((s & 1) != q) continue;
+                if (!__all_sync(0xffffffffu, mbar_wait(full_bar(s), (gi / S) & 1, abort_flag))) { ok = false; break; }
+                const int cnt = min(KT, t1 - tb);
+#pragma unroll
+                for (int u = 0; u < KT; u++) {
+                    if (u < cnt) {
+                        unsigned char* aslot = gbase + L::kA + s * L::kStageA + u * 512;
+                        const unsigned char* st = gbase + L::kCoo + (s * KT + u) * L::kCooStride;
+                        if (METCF) {  // rebuild the 16x8 operand: zero, then tile[idx] = rna(value) over the run
+                            uint32_t* tile = reinterpret_cast<uint32_t*>(aslot);
+                            reinterpret_cast<uint4*>(tile)[lane] = make_uint4(0u, 0u, 0u, 0u);
+                            __syncwarp();
+                            const int2 run = *reinterpret_cast<const int2*>(st + L::kRunAt);
+                            const int rcnt = run.y - run.x;
+                            const int* sidx = reinterpret_cast<const int*>(st);
+                            const uint32_t* sval = reinterpret_cast<const uint32_t*>(st + 128);
+                            if (lane < rcnt) tile[sidx[lane]] = sval[lane] + 0x1000u;
+                            for (int e = run.x + 32 + lane; e < run.y; e += 32)   // dense tiles: entries beyond the staged 32
+                                tile[__ldg(p.coo_idx + e)] = __float_as_uint(__ldg(p.coo_val + e)) + 0x1000u;
+                            __syncwarp();
+                        } else {
+                            const ulonglong2 m = *reinterpret_cast<const ulonglong2*>(st);
+                            reinterpret_cast<uint4*>(aslot)[lane] = mco_expand(m.x, m.y, reinterpret_cast<const uint32_t*>(st + 16), lane);
+                        }
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(ready_bar(s));
+            }
+        }
     } else if (warp == 4) {
         // ------------------------------ MMA issuer (one lane) ------------------------------------------
         if (lane == 0) {
@@ -462,7 +498,7 @@ static int launch_sweep_variant(const mask_plan* plan, SpmmArgs a, cudaStream_t 
     if (items >= ((int64_t)1 << 31)) return fail(MASK_ERR_INVALID_ARGUMENT, "too many work items");
     const int64_t resident = (int64_t)blocks_per_sm * sm_count();
     const unsigned grid = (unsigned)(items < resident ? items : resident);
-    kern<<<grid, kSweepThreads, L::kDynamicBytes, st>>>(a, plan->d_status);
+    kern<<<grid, sweep_threads(FMT), L::kDynamicBytes, st>>>(a, plan->d_status);
     MASK_CUDA_TRY(cudaGetLastError());
     return MASK_OK;
 }
