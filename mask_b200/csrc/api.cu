@@ -65,7 +65,7 @@ struct mask_session {
     cudaStream_t stream = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     // column-chunk pipeline of mask_session_spmm_host: upload, multiply and download on three streams
-    static constexpr int kMaxChunks = 8;
+    static constexpr int kMaxChunks = 16;
     cudaStream_t up = nullptr, down = nullptr;
     cudaEvent_t uploaded[kMaxChunks] = {}, k0[kMaxChunks] = {}, k1[kMaxChunks] = {}, downloaded = nullptr;
 };
