@@ -447,7 +447,7 @@ def run_gcn(args, m, bseed, dev, rank, world):
                           "data": "synthetic", "spmm_gflops_effective": 2 * 2.0 * m.nnz * N / (ms * 1e-3) / 1e9,
                           "total_gflops_effective": flops / (ms * 1e-3) / 1e9,
                           "config": {"workload": args.workload, "M": m.M, "nnz": m.nnz, "features": N, "chunks": 1 if args.gcn_fused else 4,
-                                     "panels": net.bounds}}), flush=True)
+                                     "panels": net.bounds, "panels_layer1": getattr(net, "bounds1", net.bounds)}}), flush=True)
     if args.gcn_fused:
         net.close()
     if world > 1:

@@ -23,7 +23,7 @@ import numpy as np
 import torch
 import torch.distributed as dist
 
-from .sharding import balanced_panels, nnz_balanced_panels
+from .sharding import PEER_ROW_COST_TILES, balanced_panels, minimax_panels, nnz_balanced_panels
 
 
 @dataclass
@@ -134,14 +134,28 @@ class FusedGCN2:
       ops.close()
     """
 
-    def __init__(self, csr, rank: int, world: int, device, win_prefix, hidden: int, group=None, ops=None):
+    def __init__(self, csr, rank: int, world: int, device, win_prefix, hidden: int, group=None, ops=None,
+                 peer_row_cost: float | None = None):
         self.M, self.K, self.rank, self.world, self.group = csr.M, csr.K, rank, world, group
         if csr.M != csr.K:
             raise RuntimeError("the GCN forward needs a square adjacency matrix")
+        # Layer 2 only multiplies: its panels (the rows of the output a rank returns) are balanced by SpMM
+        # cost.  Layer 1 also stores every finished row into world - 1 peers while it multiplies, and on a
+        # power-law graph equal tile counts mean very unequal row counts (the hub rows come first): its
+        # panels minimise the larger of the two costs.  A rank packs its rows once per distinct panel.
         self.bounds = balanced_panels(np.asarray(win_prefix), csr.M, world)
+        if peer_row_cost is None:
+            peer_row_cost = PEER_ROW_COST_TILES * (world - 1)
+        self.bounds1 = (minimax_panels(np.asarray(win_prefix), csr.M, world, peer_row_cost)
+                        if world > 1 and peer_row_cost > 0 else list(self.bounds))
+        self.p0, self.p1 = self.bounds1[rank], self.bounds1[rank + 1]
         self.r0, self.r1 = self.bounds[rank], self.bounds[rank + 1]
         self.ops = ops if ops is not None else _FusedDeviceOps(device, rank, world, group)
-        self.packed = self.ops.pack(csr.row_slice(self.r0, self.r1)) if self.r1 > self.r0 else None
+        self.packed1 = self.ops.pack(csr.row_slice(self.p0, self.p1)) if self.p1 > self.p0 else None
+        if (self.p0, self.p1) == (self.r0, self.r1):
+            self.packed = self.packed1
+        else:
+            self.packed = self.ops.pack(csr.row_slice(self.r0, self.r1)) if self.r1 > self.r0 else None
         self.hidden = hidden
         self.h1 = self.ops.shared_h1(csr.M, hidden)
         self.flag = torch.zeros(1, dtype=torch.int32, device=device)
@@ -158,8 +172,8 @@ class FusedGCN2:
         XW1 = X @ W1
         buf = self.h1[self.step & 1]
         self.step += 1
-        if self.packed is not None:
-            self.ops.spmm_to_all(self.packed, XW1, buf, self.r0, self.r1)
+        if self.packed1 is not None:
+            self.ops.spmm_to_all(self.packed1, XW1, buf, self.p0, self.p1)
         if self.world > 1:
             dist.all_reduce(self.flag, group=self.group)   # (stream-ordered) barrier: every panel of H1 has landed
         if self.packed is None:

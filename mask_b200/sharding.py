@@ -51,6 +51,64 @@ def spmm_cost_prefix(val_soff: np.ndarray, window_overhead_tiles: int = WINDOW_O
     return soff + window_overhead_tiles * np.arange(soff.shape[0], dtype=np.int64)
 
 
+def minimax_panels(win_prefix: np.ndarray, M: int, parts: int, row_cost: float) -> list[int]:
+    """Boundaries on window boundaries that minimise the largest panel cost when a panel costs
+    ``max(its share of win_prefix, row_cost * its rows)`` -- two resources used at the same time,
+    e.g. the tiles a rank multiplies and the finished rows it stores into its peers' memory while
+    it multiplies.  Found by bisection on the bound with a greedy feasibility walk (each panel is
+    extended as far as the bound allows, which is optimal for contiguous panels)."""
+    W = (M + WIN - 1) // WIN
+    pref = np.asarray(win_prefix).astype(np.int64)
+    assert parts >= 1 and pref.shape[0] == W + 1 and row_cost >= 0
+    win_rows = np.minimum(np.arange(W + 1, dtype=np.int64) * WIN, M)
+
+    def walk(bound: float):
+        """Window indices of the boundaries under `bound`, or None when `parts` panels do not suffice."""
+        cuts, w = [0], 0
+        for _ in range(parts):
+            if w == W:
+                cuts.append(W)
+                continue
+            by_tiles = int(np.searchsorted(pref, pref[w] + bound, side="right")) - 1
+            by_rows = int(np.searchsorted(win_rows, win_rows[w] + (bound / row_cost if row_cost > 0 else M), side="right")) - 1
+            nxt = min(by_tiles, by_rows, W)
+            if nxt <= w:
+                return None   # a single window exceeds the bound
+            cuts.append(nxt)
+            w = nxt
+        return cuts if w == W else None
+
+    lo, hi = 0.0, float(max(int(pref[W]), row_cost * M, 1))
+    best = walk(hi)
+    assert best is not None
+    for _ in range(48):
+        mid = 0.5 * (lo + hi)
+        got = walk(mid)
+        if got is None:
+            lo = mid
+        else:
+            hi, best = mid, got
+        if hi - lo <= 1e-3 * hi:
+            break
+    return [int(win_rows[w]) for w in best]
+
+
+def panel_costs(win_prefix: np.ndarray, M: int, bounds: list[int], row_cost: float) -> list[float]:
+    """``max(share of win_prefix, row_cost * rows)`` of every panel of `bounds`."""
+    pref = np.asarray(win_prefix).astype(np.int64)
+    out = []
+    for a, b in zip(bounds, bounds[1:]):
+        wa, wb = a // WIN, (b + WIN - 1) // WIN
+        out.append(max(float(pref[wb] - pref[wa]), row_cost * (b - a)))
+    return out
+
+
+# What storing one finished row of H into one peer costs, in tiles of SpMM work at the same width:
+# a row of N floats over a link that moves ~700 GB/s of 128-byte stores, against ~1.7 ns per tile at
+# N = 512 (both scale with N, so the ratio does not).
+PEER_ROW_COST_TILES = 1.72
+
+
 def nnz_balanced_panels(rowptr: np.ndarray, M: int, parts: int) -> list[int]:
     """Panels holding equal numbers of stored entries."""
     assert rowptr.shape[0] == M + 1

@@ -15,6 +15,30 @@ from mask_b200.gcn import ShardedGCN2, chunk_bounds
 from mask_b200.sharding import balanced_panels, nnz_balanced_panels
 
 
+def test_minimax_panels_against_exhaustive_search():
+    """Panels that minimise max(SpMM cost, rows stored into peers): optimal among all window-aligned
+    cuts on small cases, and equal to the plain balance when rows cost nothing."""
+    import itertools
+    from mask_b200.sharding import minimax_panels, panel_costs
+    rng = np.random.default_rng(7)
+    for _ in range(120):
+        M = int(rng.integers(1, 170))
+        W = (M + 15) // 16
+        t = rng.integers(0, 30, size=W)
+        t[:max(1, W // 4)] *= 5                       # heavy windows first, as on a power-law graph
+        pref = np.concatenate([[0], np.cumsum(t)]).astype(np.int64)
+        parts, rc = int(rng.integers(1, 5)), float(rng.choice([0.0, 0.1, 1.0, 3.0]))
+        b = minimax_panels(pref, M, parts, rc)
+        assert b[0] == 0 and b[-1] == M and len(b) == parts + 1
+        assert all(x % 16 == 0 for x in b[:-1] if x != M) and all(x <= y for x, y in zip(b, b[1:]))
+        best = min(max(panel_costs(pref, M, [0] + [min(c * 16, M) for c in cuts] + [M], rc))
+                   for cuts in itertools.combinations_with_replacement(range(W + 1), parts - 1))
+        assert max(panel_costs(pref, M, b, rc)) <= best * 1.002 + 1e-9
+    # rows dominate: equal row counts whatever the tiles
+    pref = np.concatenate([[0], np.cumsum([100, 50, 20, 5, 1, 1, 1, 1])]).astype(np.int64)
+    assert minimax_panels(pref, 128, 4, 100.0) == [0, 32, 64, 96, 128]
+
+
 def test_panels_are_window_aligned_and_balanced():
     m = G.rmat_gcn_normalised(scale=12, samples_per_node=8, seed=201)
     for parts in (1, 2, 3, 4, 8):
@@ -140,7 +164,7 @@ def _fused_rank_main(rank, world, port, shared, q):
         net = FusedGCN2(m, rank, world, torch.device("cpu"), prefix, hidden=16,
                         ops=_CpuFusedOps(rank, shared, delay=0.05 if rank == 0 else 0.0))
         outs = [net.forward(X * s, W1, W2).numpy() for s in (1.0, -2.0, 1.0, 3.0)]
-        q.put((rank, net.bounds, outs))
+        q.put((rank, net.bounds, outs, net.bounds1))
         net.close()
     finally:
         dist.destroy_process_group()
@@ -172,9 +196,13 @@ def test_fused_gcn_protocol_on_cpu_ranks(world):
         assert p.exitcode == 0
     for i, want in enumerate(wants):
         full = np.zeros_like(want)
-        for rank, bounds, outs in got:
+        for rank, bounds, outs, _ in got:
             full[bounds[rank]:bounds[rank + 1]] = outs[i]
         assert np.allclose(full, want, rtol=1e-4, atol=1e-5), i
+    # the layer that also stores into the peers is cut differently from the one that only multiplies
+    # (hub rows first: equal tiles are unequal rows), and every rank agrees on both partitions
+    assert len({tuple(b1) for _, _, _, b1 in got}) == 1 and len({tuple(b) for _, b, _, _ in got}) == 1
+    assert got[0][3] != got[0][1]
 
 
 def _gpu_rank_main(rank, world, port, q):
