@@ -143,14 +143,15 @@ def panel_bounds(m, parts: int, dev) -> list[int]:
     balanced nnz up to tile fill and row count): every rank runs the cheap window analysis of the
     device format builder on the whole matrix to get tiles per window."""
     if parts == 1:
-        return [0, m.M]
+        return [0, m.M], None
     import torch
     from mask_b200 import engine
     from mask_b200.sharding import balanced_panels, spmm_cost_prefix
     rp = torch.from_numpy(m.rowptr).to(dev)
     ci = torch.from_numpy(m.colind).to(dev)
     _, val_soff, _, _ = engine._analyze(rp, ci, m.M, m.K)
-    return balanced_panels(spmm_cost_prefix(val_soff.cpu().numpy()), m.M, parts)
+    prefix = spmm_cost_prefix(val_soff.cpu().numpy())
+    return balanced_panels(prefix, m.M, parts), prefix
 
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the dominant kernel, from
@@ -529,6 +530,7 @@ def main():
     ap.add_argument("--session-chunk", type=int, default=-1, help="columns per chunk of the host-buffer pipeline (-1 automatic, 0 off)")
     ap.add_argument("--sweep", type=int, default=1, help="1 = tcgen05 kernel except where the warp-level one measures faster, 2 = always, 0 = warp-level kernels only")
     ap.add_argument("--nslab", type=int, default=0, help="tcgen05 kernel: 128-column slabs per sweep (0 = the plan table's choice)")
+    ap.add_argument("--calibrate", type=int, default=2, help="multi-GPU: rounds of measured re-balancing of the row panels before the timed region (0 = cost model only)")
     ap.add_argument("--e2e-steps", type=int, default=3, help="0 skips the host-buffer leg")
     ap.add_argument("--nq", type=int, default=0, help="kernel variant: 32-column groups per warp (0 = default)")
     ap.add_argument("--min-blocks", type=int, default=0, help="kernel variant: occupancy target (0 = default)")
@@ -576,22 +578,57 @@ def main():
         return run_gcn(args, m, bseed, dev, rank, world)
     if args.bridge:
         return run_bridge(args, m) if rank == 0 else None
-    bounds = panel_bounds(m, world, dev)
-    r0, r1 = bounds[rank], bounds[rank + 1]
-    panel = m.row_slice(r0, r1) if world > 1 else m
+    bounds, cost_prefix = panel_bounds(m, world, dev)
     Bd, Bh, b_source = dense_operand(m.K, N, bseed, dev)
-    rp, ci, va = (torch.from_numpy(np.ascontiguousarray(x)).to(dev) for x in (panel.rowptr, panel.colind, panel.values))
 
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    packed = {"srbcrs": engine.pack_srbcrs, "metcf": engine.pack_metcf, "mco": engine.pack_mco}[args.format](rp, ci, va, panel.M, panel.K)
-    torch.cuda.synchronize()
-    pack_ms = (time.perf_counter() - t0) * 1e3
-    distinct = int(torch.unique(ci).numel()) if panel.nnz else 0
-    del rp, va
-    plan = packed.new_plan(args.policy, args.group_tiles)
+    def prepare(bounds):
+        """Packs this rank's panel and plans it."""
+        r0, r1 = bounds[rank], bounds[rank + 1]
+        panel = m.row_slice(r0, r1) if world > 1 else m
+        rp, ci, va = (torch.from_numpy(np.ascontiguousarray(x)).to(dev) for x in (panel.rowptr, panel.colind, panel.values))
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        packed = {"srbcrs": engine.pack_srbcrs, "metcf": engine.pack_metcf, "mco": engine.pack_mco}[args.format](rp, ci, va, panel.M, panel.K)
+        torch.cuda.synchronize()
+        pack_ms = (time.perf_counter() - t0) * 1e3
+        distinct = int(torch.unique(ci).numel()) if panel.nnz else 0
+        del rp, va, ci
+        plan = packed.new_plan(args.policy, args.group_tiles)
+        out = torch.empty((panel.M, N), dtype=torch.float32, device=dev)
+        return panel, packed, plan, out, pack_ms, distinct
+
+    panel, packed, plan, out, pack_ms, distinct = prepare(bounds)
+    # Measured balance: the cost model cannot see what L2 does with a panel, so the ranks time a few
+    # products, share the times and re-cut the panels from them (at most --calibrate times, outside the
+    # timed region; the matrix is packed again only on the ranks whose panel moved).
+    calibration = []
+    for _ in range(args.calibrate if world > 1 else 0):
+        from mask_b200.sharding import rebalanced_panels
+        for _ in range(2):
+            engine.spmm(packed, Bd, out=out, plan=plan)
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dist.barrier()
+        c0.record()
+        for _ in range(3):
+            engine.spmm(packed, Bd, out=out, plan=plan)
+        c1.record()
+        torch.cuda.synchronize()
+        mine = torch.tensor([c0.elapsed_time(c1) / 3.0], dtype=torch.float64, device=dev)
+        every = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        times = [float(x.item()) for x in every]
+        calibration.append([round(x, 4) for x in times])
+        if max(times) <= 1.03 * (sum(times) / world):
+            break
+        new_bounds = rebalanced_panels(cost_prefix, m.M, bounds, times)
+        moved = (new_bounds[rank], new_bounds[rank + 1]) != (bounds[rank], bounds[rank + 1])
+        bounds = new_bounds
+        if moved:
+            del packed, plan, out
+            torch.cuda.empty_cache()
+            panel, packed, plan, out, pack_ms, distinct = prepare(bounds)
+    r0, r1 = bounds[rank], bounds[rank + 1]
     info = plan.info()
-    out = torch.empty((panel.M, N), dtype=torch.float32, device=dev)
     launches_per_step = 1 + (1 if info["partial"] > 0 else 0)
     log(f"[bench] rank {rank}: rows [{r0},{r1}) nnz={panel.nnz} T={packed.T} pack {pack_ms:.1f} ms plan {info}")
 
@@ -729,6 +766,7 @@ def main():
             Bh = Bd.cpu().numpy()
         rp = torch.from_numpy(np.ascontiguousarray(panel.rowptr)).to(dev)
         va = torch.from_numpy(np.ascontiguousarray(panel.values)).to(dev)
+        ci = torch.from_numpy(np.ascontiguousarray(panel.colind)).to(dev)
         try:
             A_t = torch.sparse_csr_tensor(rp.to(torch.int64), ci.to(torch.int64), va, size=(m.M, m.K))
             for _ in range(3):
@@ -772,6 +810,7 @@ def main():
                        "partition": "row panels on window boundaries balanced by tiles + 5 per window, B replicated" if world > 1 else "none",
                        "panel_rows": [bounds[i + 1] - bounds[i] for i in range(world)],
                        "per_rank_ms": [round(x, 4) for x in per_rank_ms],
+                       "calibration_ms": calibration,
                        "l2": "no flush needed: B and C (M*N*4 bytes each) are far larger than the 126 MB L2" if 4 * m.M * N > (1 << 29)
                              else "inputs smaller than L2: the timed loop reuses them (L2-resident regime of this configuration)"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,

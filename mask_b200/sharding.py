@@ -109,6 +109,35 @@ def panel_costs(win_prefix: np.ndarray, M: int, bounds: list[int], row_cost: flo
 PEER_ROW_COST_TILES = 1.72
 
 
+def rebalanced_panels(win_prefix: np.ndarray, M: int, bounds: list[int], seconds: list[float]) -> list[int]:
+    """Re-cuts panels from measured times.  The cost model behind `win_prefix` cannot see what the
+    memory system does with a panel (on a power-law graph the hub rows at the top gather rows of B
+    with little reuse, the sparse rows at the bottom mostly gather hub columns that stay in L2), so
+    after one timed product per rank the model's cost inside old panel r is scaled by
+    seconds[r] / (model cost of panel r) and the scaled cost is cut into equal shares.  Every rank
+    must pass the same `seconds` (all-gathered) to get the same boundaries."""
+    W = (M + WIN - 1) // WIN
+    pref = np.asarray(win_prefix).astype(np.float64)
+    parts = len(bounds) - 1
+    assert pref.shape[0] == W + 1 and len(seconds) == parts and bounds[0] == 0 and bounds[-1] == M
+    wb = [min((b + WIN - 1) // WIN, W) for b in bounds]
+    scaled = np.zeros(W + 1, dtype=np.float64)
+    for r in range(parts):
+        a, b = wb[r], wb[r + 1]
+        if b <= a:
+            continue
+        seg = pref[a:b + 1] - pref[a]
+        share = float(seg[-1])
+        # a panel without model cost: spread its time over its windows
+        seg = seg * (float(seconds[r]) / share) if share > 0 else np.linspace(0.0, float(seconds[r]), b - a + 1)
+        scaled[a + 1:b + 1] = scaled[a] + seg[1:]
+    total = float(scaled[W])
+    if total <= 0:
+        return list(bounds)
+    as_int = np.round(scaled / total * float(1 << 40)).astype(np.int64)
+    return balanced_panels(np.maximum.accumulate(as_int), M, parts)
+
+
 def nnz_balanced_panels(rowptr: np.ndarray, M: int, parts: int) -> list[int]:
     """Panels holding equal numbers of stored entries."""
     assert rowptr.shape[0] == M + 1
