@@ -389,7 +389,7 @@ static int check_common(const mask_plan* plan, int32_t M, int32_t K, int32_t N, 
 
 }  // namespace mask
 
-extern "C" int mask_kernel_revision(void) { return 3; }
+extern "C" int mask_kernel_revision(void) { return 4; }
 
 extern "C" int mask_spmm_kernel_name(const mask_plan* plan, int format, int32_t N, int epilogue, char* out, size_t capacity) {
     using namespace mask;

@@ -24,22 +24,24 @@
 //   * Any N % 4 == 0: units are filled only where the column exists and the epilogue stores only
 //     such columns (tensor-memory lanes of missing columns hold garbage that is never read).
 //
-// Roles (288 threads): warps 0-3 epilogue (tensor-memory lanes 32w..32w+31 = columns of a slab),
-// warp 4 issues the MMAs (one lane), warps 5-8 produce.  A producer warp owns every fourth step WHOLE:
-// it waits for the slot, gathers the step's 16 KB with cp.async (lane -> (row, 16-byte chunk), so
-// every quarter-warp reads one contiguous 128-byte line of B and writes one bank-conflict-free row of
-// the swizzled operand), copies the tile operand(s), and -- when it comes back four steps later --
-// waits for its own copies of the previous step (cp.async.wait_group), rounds the tile values to
-// TF32 in place (each lane the 16 bytes it copied itself), issues the fence.proxy.async that
-// cp.async data needs before the tensor core may read it, and signals ready[s].  (ME-TCF and MCO
-// tiles have to be expanded from their stored form first; for them two more warps, 9-10, wait for a
-// step's copies on full[s], expand, fence and signal, 352 threads in all.)  Compared with splitting every step over all producer warps this costs a third
-// of the instructions (the per-step bookkeeping is paid by one warp, not four), needs no separate
-// preparation warps and no "landed" barrier, and the look-ahead of the column ids comes for free:
-// a warp loads the ids of its next step while it works on the current one.  Rings: ready[s]
-// (producer -> MMA), empty[s] (tcgen05.commit -> producers), acc_full / acc_empty[NACC]
-// (accumulator buffers of 16*NSLAB tensor-memory columns, so the epilogue of a window overlaps
-// the MMAs of the next ones).
+// Roles (352 threads): warps 0-3 epilogue (tensor-memory lanes 32w..32w+31 = columns of a slab),
+// warp 4 issues the MMAs (one lane), warps 5-8 copy, warps 9-10 hand over.  A copy warp owns every
+// fourth step WHOLE: it waits for the slot, gathers the step's 16 KB with cp.async (lane -> (row,
+// 16-byte chunk), so every quarter-warp reads one contiguous 128-byte line of B and writes one
+// bank-conflict-free row of the swizzled operand), copies the tile operand(s) or what they are rebuilt
+// from, and lets the copies themselves arrive on full[s] (cp.async.mbarrier.arrive.noinc): it never waits
+// for data.  The hand-over warp that owns ring stage s waits on full[s], brings the tile operand into its
+// final form (SR-BCRS: round the values to TF32 in place; ME-TCF: scatter the COO run into a zeroed tile;
+// MCO: expand mask + packed values), issues the fence.proxy.async that cp.async data needs before the
+// tensor core may read it, and signals ready[s] -- as soon as the step has landed, not when its copy warp
+// comes round again (which measured 3-6 % slower at N = 512, 13-17 % at N <= 128, and twice as slow for the
+// encodings whose hand-over is a few hundred cycles of dependent shared-memory work).  Compared with
+// splitting every step over all copy warps, one warp per step costs a third of the instructions (the
+// per-step bookkeeping is paid once, not four times), and the look-ahead of the column ids comes for
+// free: a warp loads the ids of its next step while it works on the current one.  Rings: full[s]
+// (copies -> hand-over warps), ready[s] (hand-over -> MMA), empty[s] (tcgen05.commit -> copy warps),
+// acc_full / acc_empty[NACC] (accumulator buffers of 16*NSLAB tensor-memory columns, so the epilogue of a
+// window overlaps the MMAs of the next ones).
 //
 // Every wait is bounded (about a second of SM clock).  On expiry the block raises its abort flag and
 // the plan's device status word; every role leaves its loops, the producers wait for their copies,
@@ -50,8 +52,7 @@
 
 namespace mask {
 
-// 9 warps for SR-BCRS; the COO and bitmap leaves add two warps that expand the tiles (see below)
-constexpr int sweep_threads(int fmt) { return fmt == kFmtSrbcrs ? 288 : 352; }
+constexpr int kSweepThreads = 352;   // 4 epilogue warps, the MMA warp, 4 copy warps, 2 hand-over warps
 
 template <int NSLAB, int FMT>
 struct SweepLayout {
@@ -70,7 +71,7 @@ struct SweepLayout {
     static constexpr int kA = S * kStageB;
     static constexpr int kCoo = kA + S * kStageA;
     static constexpr int kBars = kCoo + ((S * KT * kCooStride + 15) & ~15);   // empty[S], ready[S], acc_full[NACC], acc_empty[NACC], drain
-    static constexpr int kNumBars = 3 * S + 2 * kNacc + 1;   // empty, ready, full (expanding warps only), acc_full, acc_empty, drain
+    static constexpr int kNumBars = 3 * S + 2 * kNacc + 1;   // empty, ready, full, acc_full, acc_empty, drain
     static constexpr int kTmemSlot = kBars + kNumBars * 8;
     static constexpr int kAbort = kTmemSlot + 8;
     static constexpr int kBytes = kAbort + 8;
@@ -88,8 +89,8 @@ __device__ __forceinline__ bool mbar_wait_drain(uint32_t bar, uint32_t parity) {
 }
 
 template <int NSLAB, int FMT>
-__global__ void __launch_bounds__(sweep_threads(FMT), 2) spmm_sweep_kernel(const SpmmArgs p, int32_t* status) {
-    constexpr bool METCF = FMT == kFmtMetcf, MCO = FMT == kFmtMco;
+__global__ void __launch_bounds__(kSweepThreads, 2) spmm_sweep_kernel(const SpmmArgs p, int32_t* status) {
+    constexpr bool METCF = FMT == kFmtMetcf, MCO = FMT == kFmtMco, SRB = !METCF && !MCO;
     using L = SweepLayout<NSLAB, FMT>;
     constexpr int KT = L::KT, S = L::S, NACC = L::kNacc, kAccCols = L::kAccCols;
     extern __shared__ unsigned char sweep_smem_raw[];
@@ -103,11 +104,6 @@ __global__ void __launch_bounds__(sweep_threads(FMT), 2) spmm_sweep_kernel(const
     auto accf_bar = [&](int b) { return bars + 8u * (3 * S + b); };
     auto acce_bar = [&](int b) { return bars + 8u * (3 * S + NACC + b); };
     const uint32_t drain_bar = bars + 8u * (3 * S + 2 * NACC);
-    // ME-TCF and MCO tiles are expanded from their stored form, which takes a few hundred cycles of
-    // dependent shared-memory work per tile: done by the producing warp itself that put the hand-over of a
-    // step behind the issue of the next one and made those encodings twice as slow as SR-BCRS, so they
-    // get two warps of their own that wait for a step's copies (full[s]) and hand it over.
-    constexpr bool kExpandWarps = FMT != kFmtSrbcrs;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + L::kAbort);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + L::kTmemSlot);
 
@@ -119,8 +115,8 @@ __global__ void __launch_bounds__(sweep_threads(FMT), 2) spmm_sweep_kernel(const
         *abort_flag = 0;
         for (int s = 0; s < S; s++) {
             mbar_init(empty_bar(s), 1);    // tcgen05.commit
-            mbar_init(ready_bar(s), 1);    // lane 0 of the warp that hands the step over
-            mbar_init(full_bar(s), 32);    // one deferred arrive per lane of the producing warp (expanding warps only)
+            mbar_init(ready_bar(s), 1);    // lane 0 of the hand-over warp
+            mbar_init(full_bar(s), 32);    // one deferred arrive per lane of the copying warp
         }
         for (int b = 0; b < NACC; b++) {
             mbar_init(accf_bar(b), 1);     // tcgen05.commit
@@ -148,32 +144,14 @@ __global__ void __launch_bounds__(sweep_threads(FMT), 2) spmm_sweep_kernel(const
     };
 
     if (warp >= 5 && warp < 9) {
-        // ------------------------------ producers (each warp owns every fourth step) -------------------
+        // ------------------------------ copy warps (each owns every fourth step) -----------------------
         const int pw = warp - 5;
         const int lr = lane >> 3, lc = lane & 7; // row (and row + 4), 16-byte chunk
         const uint32_t off0 = (uint32_t)(lr * 128 + ((lc ^ (2 * lr)) * 16));   // 32-byte chunks swizzled by row % 4
         const uint32_t ldb_bytes = (uint32_t)(p.ldb * 4);
         const int idl = lane & (8 * KT - 1);     // which of a step's 8*KT ids this lane loads
         uint32_t gstep = 0;                      // steps of the items before the current one
-        int pend_s = -1, pend_cnt = 0;           // this warp's last step: copies issued, not yet handed to the MMA thread
         bool ok = true;
-
-        // Hands a landed step over (SR-BCRS): round the tile operand(s), make the copies visible to the
-        // tensor core's proxy, signal ready.
-        auto finish = [&](int s, int cnt) {
-#pragma unroll
-            for (int u = 0; u < KT; u++) {
-                if (u < cnt) {  // round the tile values to TF32 (nearest, ties away) in place: each lane its own 16 bytes
-                    uint4* at = reinterpret_cast<uint4*>(gbase + L::kA + s * L::kStageA + u * 512) + lane;
-                    uint4 v = *at;
-                    v.x += 0x1000u; v.y += 0x1000u; v.z += 0x1000u; v.w += 0x1000u;
-                    *at = v;
-                }
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(ready_bar(s));
-        };
 
         for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const int cb = item_cb(item);
@@ -190,7 +168,7 @@ __global__ void __launch_bounds__(sweep_threads(FMT), 2) spmm_sweep_kernel(const
             // ME-TCF / MCO: [begin, end) of the value run of tile (step j, lane), loaded ahead like the ids
             auto load_run = [&](int j) -> int2 {
                 int2 r = make_int2(0, 0);
-                if (FMT != kFmtSrbcrs) {
+                if (!SRB) {
                     const int64_t tile = (int64_t)t0 + (int64_t)j * KT + lane;
                     if (j < n_steps && lane < KT && tile < t1) {
                         if (METCF) r = __ldg(reinterpret_cast<const int2*>(p.coo_off) + tile);
@@ -215,7 +193,7 @@ __global__ void __launch_bounds__(sweep_threads(FMT), 2) spmm_sweep_kernel(const
                     id1[u] = __shfl_sync(0xffffffffu, q, u * kTileCols + lr + 4);
                 }
                 int2 run[KT];
-                if (FMT != kFmtSrbcrs) {
+                if (!SRB) {
 #pragma unroll
                     for (int u = 0; u < KT; u++) run[u] = make_int2(__shfl_sync(0xffffffffu, rq.x, u), __shfl_sync(0xffffffffu, rq.y, u));
                 }
@@ -269,23 +247,14 @@ __global__ void __launch_bounds__(sweep_threads(FMT), 2) spmm_sweep_kernel(const
                         }
                     }
                 }
-                if (kExpandWarps) {   // arrives on full[s] once every copy this lane has issued so far has landed
-                    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(full_bar(s)) : "memory");
-                } else {
-                    asm volatile("cp.async.commit_group;" ::: "memory");
-                    if (pend_s >= 0) {   // the step this warp issued four steps ago has had that long to land
-                        asm volatile("cp.async.wait_group 1;" ::: "memory");
-                        finish(pend_s, pend_cnt);
-                    }
-                    pend_s = s; pend_cnt = cnt;
-                }
+                // arrives on full[s] once every copy this lane has issued so far has landed
+                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(full_bar(s)) : "memory");
             }
             gstep += (uint32_t)n_steps;
         }
-        asm volatile("cp.async.wait_all;" ::: "memory");
-        if (ok && pend_s >= 0) finish(pend_s, pend_cnt);
+        asm volatile("cp.async.wait_all;" ::: "memory");   // nothing of this warp's is in flight when the block leaves
     } else if (warp >= 9) {
-        // ------------------------------ expanding warps (ME-TCF / MCO only; alternate steps) -----------
+        // ------------------------------ hand-over warps (ring stages split between the two) ------------
         const int q = warp - 9;
         uint32_t gi = 0;
         bool ok = true;
@@ -317,9 +286,14 @@ __global__ void __launch_bounds__(sweep_threads(FMT), 2) spmm_sweep_kernel(const
                             for (int e = run.x + 32 + lane; e < run.y; e += 32)   // dense tiles: entries beyond the staged 32
                                 tile[__ldg(p.coo_idx + e)] = __float_as_uint(__ldg(p.coo_val + e)) + 0x1000u;
                             __syncwarp();
-                        } else {
+                        } else if (MCO) {
                             const ulonglong2 m = *reinterpret_cast<const ulonglong2*>(st);
                             reinterpret_cast<uint4*>(aslot)[lane] = mco_expand(m.x, m.y, reinterpret_cast<const uint32_t*>(st + 16), lane);
+                        } else {   // dense tile: round to TF32 (nearest, ties away) in place
+                            uint4* at = reinterpret_cast<uint4*>(aslot) + lane;
+                            uint4 v = *at;
+                            v.x += 0x1000u; v.y += 0x1000u; v.z += 0x1000u; v.w += 0x1000u;
+                            *at = v;
                         }
                     }
                 }
@@ -455,7 +429,7 @@ __global__ void __launch_bounds__(sweep_threads(FMT), 2) spmm_sweep_kernel(const
                     asm volatile("" : "+r"(row0));   // keeps the 16 row offsets from being hoisted out of this loop into registers
 #pragma unroll
                     for (int i = 0; i < 16; i++) {
-                        const int r = FMT != kFmtSrbcrs ? i : (i ^ (i >> 3));   // MMA-N index -> window row (SR-BCRS: rows 8..15 swapped pairwise)
+                        const int r = !SRB ? i : (i ^ (i >> 3));   // MMA-N index -> window row (SR-BCRS: rows 8..15 swapped pairwise)
                         if (r < rows_ok) {
                             const int64_t off = slot >= 0 ? (int64_t)r * p.N
                                                           : (int64_t)(p.row_map ? p.row_map[row0 + r] : row0 + r) * p.ldc;
@@ -498,7 +472,7 @@ static int launch_sweep_variant(const mask_plan* plan, SpmmArgs a, cudaStream_t 
     if (items >= ((int64_t)1 << 31)) return fail(MASK_ERR_INVALID_ARGUMENT, "too many work items");
     const int64_t resident = (int64_t)blocks_per_sm * sm_count();
     const unsigned grid = (unsigned)(items < resident ? items : resident);
-    kern<<<grid, sweep_threads(FMT), L::kDynamicBytes, st>>>(a, plan->d_status);
+    kern<<<grid, kSweepThreads, L::kDynamicBytes, st>>>(a, plan->d_status);
     MASK_CUDA_TRY(cudaGetLastError());
     return MASK_OK;
 }
