@@ -358,7 +358,7 @@ int mask_spmm_srbcrs_static_scratch(const mask_plan* plan, const int32_t* d_val_
                                     float* d_C, int64_t ldc, int epilogue, void* stream);
 
 /* Development knobs for kernel variants, process-wide: "sweep" (1 = persistent tcgen05 kernel except
- * where the warp-level one measures faster (N < 96), 2 = always, 0 = warp-level kernels only),
+ * where the warp-level one measures faster (N < 80), 2 = always, 0 = warp-level kernels only),
  * "nslab" (tcgen05 kernel: 128-column slabs per sweep, 1 / 2 / 4; 0 = the plan table's choice),
  * "tma" (1 = the TMA-fed kernel for plans prepared with mask_plan_prepare_values), and for the
  * warp-level kernels "nq" (32-column groups per warp: 1, 2, 4; 0 = chosen from N), "min_blocks"

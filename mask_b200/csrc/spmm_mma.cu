@@ -41,6 +41,7 @@ static int g_tune_min_blocks = 0;
 static int g_tune_async = 1;   // 1 = shared-memory ring fed by cp.async (SR-BCRS), 0 = register pipeline
 static int g_tune_stages = 0;
 extern int g_session_chunk_cols;      // api.cu: column chunks of the host-buffer pipeline
+constexpr int kNarrowN = 80;   // below: the warp-level ring kernel (see launch_spmm)
 static int g_tune_sweep = 1;   // 1 = persistent tcgen05 kernel except where the warp-level one measures faster, 2 = always, 0 = warp-level kernels only
 static int g_tune_nslab = 0;   // persistent kernel: 128-column slabs per column block (0 = the plan's choice)
 static int g_tune_tma = 0;     // 1 = the TMA-fed kernel where the plan holds rounded tile values (spmm_tma.cu); measured slower, off by default
@@ -323,10 +324,10 @@ static int launch_spmm(const mask_plan* plan, SpmmArgs a, cudaStream_t st) {
         if (rc != MASK_OK) return rc;
         return launch_fixup(plan, a, st);
     }
-    // Narrow products: below about 96 columns a tile's one half-empty 128-column MMA costs more than
-    // the warp-level MMAs of the shared-memory ring kernel (measured crossover on a 2^22-node power-law
-    // graph: N = 64 5.8 against 7.5 ms, N = 128 9.0 against 7.9 ms).
-    if (FMT == kFmtSrbcrs && g_tune_sweep == 1 && N < 96 && g_tune_async != 0) {
+    // Narrow products: below about 80 columns a tile's one mostly empty 128-column MMA costs more than
+    // the warp-level MMAs of the shared-memory ring kernel (measured on a 2^22-node power-law graph:
+    // N = 64 5.33 against 6.33 ms, N = 80 6.57 against 6.48 ms, N = 128 6.8 ms for the tcgen05 kernel).
+    if (FMT == kFmtSrbcrs && g_tune_sweep == 1 && N < kNarrowN && g_tune_async != 0) {
         int rc = launch_spmm_async(plan, a, st, g_tune_nq, g_tune_stages);
         if (rc != MASK_OK) return rc;
         return launch_fixup(plan, a, st);
@@ -398,7 +399,7 @@ extern "C" int mask_spmm_kernel_name(const mask_plan* plan, int format, int32_t 
     static const char* const fmt_name[] = {"srbcrs", "metcf", "mco"};
     if (format == kFmtSrbcrs && (epilogue & MASK_NUMERICS_TF32X3)) {
         snprintf(out, capacity, "spmm_async_kernel<tf32x3>");
-    } else if (format == kFmtSrbcrs && g_tune_sweep == 1 && N < 96 && g_tune_async != 0) {
+    } else if (format == kFmtSrbcrs && g_tune_sweep == 1 && N < kNarrowN && g_tune_async != 0) {
         snprintf(out, capacity, "spmm_async_kernel<%s>", fmt_name[format]);
     } else if (g_tune_sweep != 0) {
         int nslab = g_tune_nslab != 0 ? g_tune_nslab : plan->nslab;
