@@ -277,6 +277,36 @@ def test_medium_rmat_against_oracle(oracle_mod):
     _assert_close(oracle_mod, m, B, out2.cpu().numpy())
 
 
+@pytest.mark.parametrize("fmt", ["srbcrs", "metcf", "mco"])
+def test_long_persistent_runs_every_encoding(oracle_mod, fmt):
+    """A 2^18-node power-law graph: every resident block walks its rings some two thousand times per
+    launch, for the 6-stage ring of SR-BCRS and the 5-stage ring of the compact encodings, at one and
+    two slabs per sweep, several launches each.  Hand-over faults that need many ring revolutions to
+    show (a waiter that misses a barrier phase) end in a bounded wait giving up, so the plan's status
+    word is checked beside the sampled rows."""
+    import torch
+    from mask_b200 import engine, generators as G
+    m, bseed = G.make_workload("rmat20_gcn", scale=18)
+    rp, ci, va = _dev(m)
+    p = {"srbcrs": engine.pack_srbcrs, "metcf": engine.pack_metcf, "mco": engine.pack_mco}[fmt](rp, ci, va, m.M, m.K)
+    rng = np.random.Generator(np.random.PCG64(5))
+    rows = np.unique(np.concatenate([rng.integers(0, m.M, size=2048), np.arange(0, 48), np.arange(m.M - 16, m.M)]))
+    rows_d = torch.from_numpy(rows).cuda()
+    for N in (512, 128):
+        B = G.dense_normal(m.K, N, bseed + N)
+        Bd = torch.from_numpy(B).cuda()
+        ref, absp = oracle_mod.spmm_rows(m.rowptr, m.colind, m.values, B, rows)
+        plan = p.new_plan("auto")
+        out = torch.empty((m.M, N), device="cuda")
+        for _ in range(4):
+            out.fill_(float("nan"))
+            engine.spmm(p, Bd, out=out, plan=plan)
+            assert plan.status() == 0
+            bad, worst = oracle_mod.check_tolerance(out[rows_d].cpu().numpy(), ref, absp, RTOL, ATOL)
+            assert bad == 0, (N, worst)
+        assert not bool(torch.isnan(out[:: 997]).any())
+
+
 @pytest.mark.parametrize("name,N,gt", [("m1", 512, 0), ("m17", 512, 0), ("m33_empty_window", 512, 0), ("all_empty", 512, 0),
                                        ("hub_rows", 512, 3), ("hub_rows", 1024, 0), ("rmat12u", 512, 0),
                                        ("rmat12u", 512, 200), ("stencil8", 1024, 0), ("three_four_tiles", 512, 1),
