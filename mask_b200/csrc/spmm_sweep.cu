@@ -1,6 +1,6 @@
 // Persistent tcgen05 SpMM: one resident grid sweeps the matrix once per block of 128*NSLAB columns.
 //
-// The product is issued transposed, as in spmm_umma.cu: for every tile t and 128-column slab,
+// The product is issued transposed: for every tile t and 128-column slab,
 //     D^T[128 columns x 16 rows] += Bg^T[128 x 8] * Atile^T[8 x 16]      (tcgen05.mma kind::tf32)
 // with the 8 gathered rows of B as the MN-major operand (128-byte swizzle, 32-byte base) and the
 // stored 16x8 tile as the K-major SWIZZLE_32B operand, accumulators in tensor memory.
@@ -19,7 +19,7 @@
 //     regard to window boundaries; only the MMA issuer and the epilogue know about windows.
 //   * The block lives for the whole launch: barriers, tensor memory and the pipeline are set up
 //     once, not once per group, and groups can be as long as the planner likes.
-//   * Column ids are not staged in shared memory: a producer warp loads the ids of a step with one
+//   * Column ids are not staged in shared memory: a copy warp loads the ids of a step with one
 //     coalesced load and hands them out with shuffles.
 //   * Any N % 4 == 0: units are filled only where the column exists and the epilogue stores only
 //     such columns (tensor-memory lanes of missing columns hold garbage that is never read).
