@@ -121,6 +121,9 @@ class FusedGCN2:
     path, only a one-word all-reduce as the barrier between the layers.  Layer 2 is reassociated,
     ``out = (A·H1)·W2``, so that what the SpMM produces is what the peers need.
 
+    The two layers are partitioned separately (``bounds1`` for layer 1, ``bounds`` for layer 2 and the
+    rows a rank returns): layer 1 pays for the rows it stores into its peers as well as for its tiles.
+
     H1 is double-buffered: a rank that races ahead into the next forward writes the other buffer,
     and cannot get a second forward ahead because of the barrier, so no rank's layer-2 reads are
     overwritten.
