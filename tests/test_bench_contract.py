@@ -55,3 +55,28 @@ def test_gpu_arm_line():
     ck = d["clocks"]
     assert ck["sm_mhz"] > 0 and ck["sm_max_mhz"] >= ck["sm_mhz"] and isinstance(ck["reasons"], list)
     assert d["kernel_status"] == 0 and d["verified"]["violations"] == 0
+
+
+def test_verification_sampler_on_host_tensors():
+    """bench.VerifySample with CPU tensors: the whole matrix, or seeded rows plus the heaviest windows within
+    the entry budget; a single corrupted element of a sampled row is reported."""
+    import numpy as np
+    import torch
+    sys.path.insert(0, ROOT)
+    import bench
+    import oracle
+    from mask_b200 import generators as G
+    m = G.rmat_gcn_normalised(scale=11, samples_per_node=8, seed=201)
+    B = torch.from_numpy(G.dense_normal(m.K, 32, 5))
+    soff = oracle.pack_srbcrs(m.M, m.rowptr, m.colind, m.values)["val_soff"]
+    ref = torch.from_numpy(oracle.spmm_f32(m.M, m.rowptr, m.colind, m.values, B.numpy()))
+    full = bench.VerifySample(oracle, m, soff, B, seed=7, n_random=100, n_heavy=4, full=True)
+    assert full.rows.size == m.M and full.check(ref)[0] == 0
+    part = bench.VerifySample(oracle, m, soff, B, seed=7, n_random=300, n_heavy=40, full=False, heavy_entries=4000)
+    assert 300 * 0.8 < part.rows.size < m.M and "heaviest windows" in part.how
+    heaviest = int(np.argmax(np.diff(soff)))
+    assert set(range(heaviest * 16, heaviest * 16 + 16)) <= set(part.rows.tolist())   # the heaviest window is always in
+    assert part.check(ref)[0] == 0
+    bad = ref.clone()
+    bad[int(part.rows[5]), 3] += 1.0
+    assert part.check(bad)[0] == 1 and part.check_host(bad[torch.from_numpy(part.rows)].numpy())[0] == 1
