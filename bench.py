@@ -234,6 +234,28 @@ class VerifySample:
         return self.oracle.check_tolerance(np.ascontiguousarray(rows_host), self.ref, self.absp)
 
 
+def packing_parity(oracle, panel, packed, max_entries: int = 1 << 24):
+    """Byte comparison of the device-built SR-BCRS arrays with the CPU oracle's packing of the same rows: the
+    whole panel, or its leading windows holding at most `max_entries` stored entries (windows are packed
+    independently, so the leading windows of the panel's arrays are the arrays of the leading rows).
+    Returns (mismatching arrays, windows compared, tiles compared)."""
+    rows = panel.M
+    if panel.nnz > max_entries:
+        rows = max(16, int(np.searchsorted(panel.rowptr, max_entries, side="right") - 1) // 16 * 16)
+    rp = np.ascontiguousarray(panel.rowptr[:rows + 1])
+    n = int(rp[-1])
+    want = oracle.pack_srbcrs(rows, rp, np.ascontiguousarray(panel.colind[:n]), np.ascontiguousarray(panel.values[:n]))
+    W, T = (rows + 15) // 16, int(want["T"])
+    got = {"val_soff": packed.val_soff[:W + 1], "val_sidx": packed.val_sidx[:8 * T], "val_block_val": packed.val_block_val[:128 * T]}
+    bad = []
+    for name, dev_arr in got.items():
+        a = dev_arr.cpu().numpy()
+        b = want[name]
+        if a.shape != b.shape or not np.array_equal(a.view(np.uint32), b.view(np.uint32)):
+            bad.append(name)
+    return bad, W, T
+
+
 def cpu_baseline(m, N, Bd, Bh):
     """The oracle's host FP32 SpMM (CPU port of the reference's cpu_spmm) with every host thread on
     a bounded sample: the leading rows of the matrix holding at most 2^26 stored entries."""
@@ -698,6 +720,17 @@ def main():
                     "tolerance": "|C-Cref| <= 2e-3*(|A|.|B|) + 1e-6"}
         if bad:
             log(f"[bench] rank {rank}: VERIFICATION FAILED: {bad} elements outside tolerance")
+        if args.format == "srbcrs":   # the packed arrays themselves, byte for byte against the oracle's packing
+            wrong, w_cmp, t_cmp = packing_parity(oracle, panel, packed)
+            pk = torch.tensor([len(wrong), w_cmp, t_cmp], dtype=torch.int64, device=dev)
+            if world > 1:
+                dist.all_reduce(pk, op=dist.ReduceOp.SUM)
+            verified["packing"] = {"mismatching_arrays": int(pk[0].item()), "windows_compared": int(pk[1].item()),
+                                   "tiles_compared": int(pk[2].item()),
+                                   "how": "val_soff, val_sidx, val_block_val of every rank's panel (leading windows up to 2^24 "
+                                          "stored entries) byte for byte against the CPU oracle's packing"}
+            if wrong:
+                log(f"[bench] rank {rank}: PACKING MISMATCH in {wrong}")
 
     # ---- end to end with host buffers ----
     e2e = None
